@@ -54,6 +54,7 @@ class LayerCache:
     state: Optional[torch.Tensor]  # [max_slots, *shape]
     writes: bool = True
     window: Optional[int] = None
+    states: Optional[Dict[str, torch.Tensor]] = None  # a state made of named tensors, each [max_slots, *shape]
 
     @property
     def k(self) -> Optional[torch.Tensor]:
@@ -131,6 +132,7 @@ class CacheManager:
         self._group_of: List[Optional[_Group]] = []
         self._pages: List[Dict[str, torch.Tensor]] = []
         self._state: List[Optional[torch.Tensor]] = []
+        self._named_state: List[Optional[Dict[str, torch.Tensor]]] = []
         for idx, cs in enumerate(cache_specs):
             g = None
             st = None
@@ -147,8 +149,16 @@ class CacheManager:
                         raise CacheError(f"cache {idx}: two paged tensors are named {ts.name!r}")
                     pages[ts.name] = torch.zeros((g.pool.n_pages, *ts.page_shape(self.page_size)),
                                                  dtype=ts.dtype or dtype, device=self.device)
+            named = None
             if cs is not None and cs.state is not None:
-                st = torch.zeros((self.max_slots, *cs.state.shape), dtype=cs.state.dtype, device=self.device)
+                if cs.state.parts:
+                    named = {n: torch.zeros((self.max_slots, *shape), dtype=cs.state.dtype, device=self.device)
+                             for n, shape in cs.state.parts}
+                    if len(named) != len(cs.state.parts):
+                        raise CacheError(f"cache {idx}: two state tensors share a name")
+                else:
+                    st = torch.zeros((self.max_slots, *cs.state.shape), dtype=cs.state.dtype, device=self.device)
+            self._named_state.append(named)
             self._group_of.append(g)
             self._pages.append(pages)
             self._state.append(st)
@@ -185,6 +195,9 @@ class CacheManager:
             return None
         for st in self._state:
             if st is not None:
+                st[slot].zero_()
+        for named in self._named_state:
+            for st in (named or {}).values():
                 st[slot].zero_()
         return slot
 
@@ -282,6 +295,7 @@ class CacheManager:
             state=self._state[cache_index],
             writes=writes,
             window=g.window if g is not None else None,
+            states=self._named_state[cache_index],
         )
 
     def kv_bytes(self) -> int:

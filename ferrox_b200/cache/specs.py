@@ -6,6 +6,7 @@ how far back the mixer reads, which decides when pages can be given back), a blo
 of fixed size per request (:class:`StateSpec`; recurrent mixers), both, or nothing.
 Keys and values of an attention layer are the built-in case (:func:`KvCacheSpec`);
 a mixer that keeps one vector per position, or three tensors, names them itself.
+A state may be one tensor or several named ones (``StateSpec.parts``).
 
 The reference's counterpart is the ``Engine::State`` associated type
 (crates/ferrox-models/src/engine.rs:44-53): ``Vec<KvCache>`` for its decoder, a
@@ -53,8 +54,13 @@ def KvCacheSpec(n_kv_heads: int, head_dim: int, window: Optional[int] = None) ->
 
 @dataclass(frozen=True)
 class StateSpec:
-    shape: Tuple[int, ...]
+    """A block of fixed size per request.  ``parts``: the block is a tuple of named tensors instead of one
+    (a matrix state and the tail of a short convolution, or the states of several mixers that share a layer);
+    ``shape`` is then ignored and ``LayerCache.states[name]`` holds each."""
+
+    shape: Tuple[int, ...] = ()
     dtype: torch.dtype = torch.float32
+    parts: Tuple[Tuple[str, Tuple[int, ...]], ...] = ()
 
 
 @dataclass(frozen=True)

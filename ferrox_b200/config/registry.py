@@ -1,6 +1,6 @@
 """The one registry: architecture name -> (typed configuration, model description).
 
-``config.json`` names its architecture in ``architectures[0]``; everything else in
+``config.json`` names its architecture in ``architectures[0]`` (or in ``architecture``); everything else in
 the framework (loader, engine, trace replay, command line) asks this registry for
 the model that belongs to that name.  An unknown name fails closed with the list of
 known ones, as the reference's capability table does
@@ -36,8 +36,10 @@ def known_architectures() -> list:
 
 def architecture_of(obj: dict, where: str = "config.json") -> Architecture:
     archs = obj.get("architectures")
+    if archs is None and isinstance(obj.get("architecture"), str):
+        archs = [obj["architecture"]]     # files that name their one architecture under 'architecture'
     if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-        raise ConfigError(f"{where}: 'architectures' must be a non-empty list of names")
+        raise ConfigError(f"{where}: 'architectures' must be a non-empty list of names (or 'architecture' a name)")
     name = archs[0]
     if name not in _ARCHITECTURES:
         raise ConfigError(

@@ -23,6 +23,8 @@ int fx_rmsnorm(const float* x, const int* rows, const void* w, int w_dtype, floa
                int n_rows, int hidden, void* stream);
 int fx_silu_mul(const void* gu, long ld_in, void* out, long ld_out, int dtype, const int* n_rows_dev, int rows, int n,
                 void* stream);
+int fx_glu_mul(const void* gu, long ld_in, void* out, long ld_out, int dtype, const int* n_rows_dev, int rows, int n,
+               int act, void* stream);   // act(gate) * up; act 0: SiLU, 1: ReLU
 int fx_rope_kv_write(void* qkv, int dtype, long ld, const int* positions, const int* token_seq, const int* seq_slot,
                      const float* inv_freq, const float* cos_sin, int rotary_dim, int pairing, void* k_pages, void* v_pages, const int* block_table,
                      int table_width, int page_size, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
@@ -35,7 +37,7 @@ int fx_residual_add(float* h, const void* y, int dtype, long n, void* stream);
 int fx_paged_attention(const void* q, long ldq, const void* k_pages, const void* v_pages, int dtype,
                        const int* block_table, int table_width, int page_size, const int* positions,
                        const int* token_seq, const int* seq_slot, void* out, long ldo, int n_tokens, int n_heads,
-                       int n_kv_heads, int head_dim, int window, float scale, void* stream);
+                       int n_kv_heads, int head_dim, int window, float scale, float softcap, void* stream);
 
 int fx_prefill_attention_tc(const void* q, long ldq, int n_tokens, const void* k_pages, const void* v_pages, int n_pages,
                             const int* block_table, int table_width, int page_size, const int* items, int n_items,
@@ -126,6 +128,29 @@ int fx_repetition_penalty(float* work, long ld, int n_rows, int vocab, const int
                           const float* penalty, void* stream);
 int fx_sample(float* work, long ld, int n_rows, int vocab, const float* temperature, const int* top_k,
               const float* top_p, const float* draw, int* out, void* stream);
+
+// Layer norm without bias (layernorm.cu): out = (x - mean) / sqrt(var + eps) * w over rows of the 32-bit residual
+// stream (`rows` optional: which rows; out may be x itself).  fx_layernorm_residual: z = s1 y1 (+ s2 y2);
+// h += ln(z) w_post; and, if w_next is given, x_out = ln(h) w_next on the new rows.  fx_scale: x *= scale.
+int fx_layernorm(const float* x, const int* rows, const void* w, int w_dtype, float eps, void* out, int out_dtype,
+                 int n_rows, int hidden, void* stream);
+int fx_layernorm_residual(float* h, const void* y1, int y1_dtype, float s1, const void* y2, int y2_dtype, float s2,
+                          const void* w_post, int wp_dtype, float eps, const void* w_next, int wn_dtype, float eps_next,
+                          void* x_out, int x_dtype, int n_rows, int hidden, void* stream);
+int fx_scale(float* x, long n, float scale, void* stream);
+
+// Mixers with a matrix state per (request, head) (linear_state.cu).  The state is [slots, H, V, D] 32-bit.
+int fx_delta_prep(const void* proj, int dtype, long ldp, const void* conv_w, int cw_dtype, int taps, const float* tail,
+                  const float* ba, long ldba, const float* a_log, const float* dt_bias, const int* token_seq,
+                  const int* seq_slot, float* out, float* beta, float* g, int n_tokens, int G, int D, int H, int V,
+                  void* stream);
+int fx_conv_tail_update(const void* proj, int dtype, long ldp, int channels, int taps, float* tail, const int* token_seq,
+                        const int* seq_slot, int n_tokens, int n_entries, void* stream);
+int fx_state_scan(const void* q, long ldq, const void* k, long ldk, const void* v, long ldv, int dtype, int act,
+                  const float* g, long g_ld, const float* beta, float* state, float* out, long ldo, const int* token_seq,
+                  const int* seq_slot, int n_tokens, int n_entries, int H, int G, int D, int V, void* stream);
+int fx_gated_group_norm(const float* x, const void* gate, int gate_dtype, long ldg, const void* w, int w_dtype, float eps,
+                        int act, void* out, int out_dtype, int n_tokens, int groups, int width, void* stream);
 
 #ifdef __cplusplus
 }

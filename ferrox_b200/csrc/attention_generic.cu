@@ -33,7 +33,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_kernel(
     const T* __restrict__ q, long ldq, const T* __restrict__ k_pages, const T* __restrict__ v_pages,
     const int* __restrict__ block_table, int table_width, int page_size,
     const int* __restrict__ positions, const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
-    T* __restrict__ out, long ldo, int n_heads, int n_kv_heads, int head_dim, int window, float scale)
+    T* __restrict__ out, long ldo, int n_heads, int n_kv_heads, int head_dim, int window, float scale, float softcap)
 {
     __shared__ float q_s[WARPS][MAX_D];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -67,6 +67,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_kernel(
             float dot = 0.f;
             for (int i = 0; i < head_dim; ++i) dot = fmaf(q_s[warp][i], to_f32(kr[i]), dot);
             s = dot * scale;
+            if (softcap > 0.f) s = softcap * tanhf(s / softcap);   // soft cap: scores stay inside (-cap, cap)
         }
         const float m_new = fmaxf(m, warp_max(s));
         if (m_new == -INFINITY) continue;  // no key of this block is readable (uniform across the warp)
@@ -102,7 +103,8 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_kernel(
 extern "C" int fx_paged_attention(const void* q, long ldq, const void* k_pages, const void* v_pages, int dtype,
                                   const int* block_table, int table_width, int page_size, const int* positions,
                                   const int* token_seq, const int* seq_slot, void* out, long ldo, int n_tokens,
-                                  int n_heads, int n_kv_heads, int head_dim, int window, float scale, void* stream)
+                                  int n_heads, int n_kv_heads, int head_dim, int window, float scale, float softcap,
+                                  void* stream)
 {
     if (n_tokens <= 0) return FX_OK;
     if (head_dim > MAX_D || head_dim <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads) return FX_ERR_SIZE;
@@ -111,11 +113,11 @@ extern "C" int fx_paged_attention(const void* q, long ldq, const void* k_pages, 
     if (dtype == FX_F32)
         paged_attention_kernel<float><<<grid, WARPS * 32, 0, s>>>((const float*)q, ldq, (const float*)k_pages,
             (const float*)v_pages, block_table, table_width, page_size, positions, token_seq, seq_slot, (float*)out,
-            ldo, n_heads, n_kv_heads, head_dim, window, scale);
+            ldo, n_heads, n_kv_heads, head_dim, window, scale, softcap);
     else if (dtype == FX_BF16)
         paged_attention_kernel<bf16><<<grid, WARPS * 32, 0, s>>>((const bf16*)q, ldq, (const bf16*)k_pages,
             (const bf16*)v_pages, block_table, table_width, page_size, positions, token_seq, seq_slot, (bf16*)out,
-            ldo, n_heads, n_kv_heads, head_dim, window, scale);
+            ldo, n_heads, n_kv_heads, head_dim, window, scale, softcap);
     else return FX_ERR_DTYPE;
     return fx_launch_status();
 }

@@ -73,14 +73,14 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
 // silu(x) = x / (1 + exp(-x)) (reference: matmul.rs:268-280).
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, long ld_in, T* __restrict__ out, long ld_out,
-                                const int* __restrict__ n_rows_dev, int rows, int n)
+                                const int* __restrict__ n_rows_dev, int rows, int n, int act)
 {
     const long total = (long)(n_rows_dev ? *n_rows_dev : rows) * n;
     for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
         const long r = i / n; const int c = (int)(i - r * n);
         const float g = to_f32(gu[r * ld_in + c]);
         const float u = to_f32(gu[r * ld_in + n + c]);
-        out[r * ld_out + c] = from_f32<T>(g / (1.0f + expf(-g)) * u);
+        out[r * ld_out + c] = from_f32<T>((act ? fmaxf(g, 0.f) : g / (1.0f + expf(-g))) * u);   // act 1: ReLU
     }
 }
 
@@ -493,15 +493,25 @@ extern "C" int fx_rmsnorm(const float* x, const int* rows, const void* w, int w_
     return fx_launch_status();
 }
 
+extern "C" int fx_glu_mul(const void* gu, long ld_in, void* out, long ld_out, int dtype, const int* n_rows_dev,
+                          int rows, int n, int act, void* stream);
+
 extern "C" int fx_silu_mul(const void* gu, long ld_in, void* out, long ld_out, int dtype, const int* n_rows_dev,
                            int rows, int n, void* stream)
+{
+    return fx_glu_mul(gu, ld_in, out, ld_out, dtype, n_rows_dev, rows, n, 0, stream);
+}
+
+// act(gate) * up over rows of [gate | up]; act 0: SiLU, 1: ReLU.
+extern "C" int fx_glu_mul(const void* gu, long ld_in, void* out, long ld_out, int dtype, const int* n_rows_dev,
+                          int rows, int n, int act, void* stream)
 {
     if (rows <= 0 || n <= 0) return FX_OK;
     cudaStream_t s = (cudaStream_t)stream;
     long blocks = fx_cdiv((long)rows * n, 256);
     if (blocks > fx_sm_count() * 16L) blocks = fx_sm_count() * 16L;
-    if (dtype == FX_F32) silu_mul_kernel<float><<<(unsigned)blocks, 256, 0, s>>>((const float*)gu, ld_in, (float*)out, ld_out, n_rows_dev, rows, n);
-    else if (dtype == FX_BF16) silu_mul_kernel<bf16><<<(unsigned)blocks, 256, 0, s>>>((const bf16*)gu, ld_in, (bf16*)out, ld_out, n_rows_dev, rows, n);
+    if (dtype == FX_F32) silu_mul_kernel<float><<<(unsigned)blocks, 256, 0, s>>>((const float*)gu, ld_in, (float*)out, ld_out, n_rows_dev, rows, n, act);
+    else if (dtype == FX_BF16) silu_mul_kernel<bf16><<<(unsigned)blocks, 256, 0, s>>>((const bf16*)gu, ld_in, (bf16*)out, ld_out, n_rows_dev, rows, n, act);
     else return FX_ERR_DTYPE;
     return fx_launch_status();
 }

@@ -41,6 +41,7 @@ struct Tc2Args {
     const void* bias; int bias_dtype;
     int M, N, K;
     int gate_up_offset;
+    int act;                        // gated: 0 SiLU, 1 ReLU on the gate
     int gated;
     int* status;
 };
@@ -239,7 +240,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc2_kernel(const __grid_cons
                 for (int j = 0; j < 32; ++j) {
                     float x = __uint_as_float(r[j]);
                     if (a.bias) x += bias_s[quad][c * 32 + j];
-                    if (GATED) x = __fdividef(x, 1.0f + __expf(-x)) * __uint_as_float(u[j]);
+                    if (GATED) x = (a.act ? fmaxf(x, 0.f) : __fdividef(x, 1.0f + __expf(-x))) * __uint_as_float(u[j]);
                     v[j] = x;
                 }
                 if (fast) {
@@ -327,7 +328,7 @@ bool make_map(CUtensorMap* map, const void* ptr, uint64_t K, uint64_t rows, uint
 }  // namespace
 
 // X [M, K] and W [w_rows, K] bfloat16; C bfloat16 or float32.  gated: W holds gate rows [0, N) and up rows
-// [gate_up_offset, gate_up_offset + N), C = silu(gate) * up.  Dense products only (no groups).
+// [gate_up_offset, gate_up_offset + N), C = act(gate) * up (gated 1: SiLU, 2: ReLU).  Dense products only (no groups).
 extern "C" int fx_gemm_tc2(const void* X, long ldx, const void* W, long ldw, int w_rows, const void* bias, int bias_dtype,
                            void* C, int c_dtype, long ldc, int accumulate, int M, int N, int K, int gated,
                            int gate_up_offset, int* status, void* stream)
@@ -339,7 +340,7 @@ extern "C" int fx_gemm_tc2(const void* X, long ldx, const void* W, long ldw, int
     Tc2Args a;
     a.C = C; a.ldc = ldc; a.c_dtype = c_dtype; a.accumulate = accumulate;
     a.bias = bias; a.bias_dtype = bias_dtype;
-    a.M = M; a.N = N; a.K = K; a.gate_up_offset = gate_up_offset; a.gated = gated; a.status = status;
+    a.M = M; a.N = N; a.K = K; a.gate_up_offset = gate_up_offset; a.gated = gated; a.act = gated == 2; a.status = status;
     CUtensorMap ma, mb;
     if (!make_map(&ma, X, (uint64_t)K, (uint64_t)M, (uint64_t)ldx, BM)) return FX_ERR_SIZE;
     if (!make_map(&mb, W, (uint64_t)K, (uint64_t)w_rows, (uint64_t)ldw, BNH)) return FX_ERR_SIZE;

@@ -50,7 +50,15 @@ _SIGNATURES = {
     "fx_moe_combine": [_P, _P, _I, _P, _P, _I, _P, _P, _L, _I, _I, _P],
     "fx_moe_combine_norm": [_P, _P, _I, _P, _P, _I, _P, _P, _L, _I, _I, _P, _I, _F, _P, _P],
     "fx_residual_add": [_P, _P, _I, _L, _P],
-    "fx_paged_attention": [_P, _L, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _F, _P],
+    "fx_paged_attention": [_P, _L, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _F, _F, _P],
+    "fx_glu_mul": [_P, _L, _P, _L, _I, _P, _I, _I, _I, _P],
+    "fx_layernorm": [_P, _P, _P, _I, _F, _P, _I, _I, _I, _P],
+    "fx_layernorm_residual": [_P, _P, _I, _F, _P, _I, _F, _P, _I, _F, _P, _I, _F, _P, _I, _I, _I, _P],
+    "fx_scale": [_P, _L, _F, _P],
+    "fx_delta_prep": [_P, _I, _L, _P, _I, _I, _P, _P, _L, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "fx_conv_tail_update": [_P, _I, _L, _I, _I, _P, _P, _P, _I, _I, _P],
+    "fx_state_scan": [_P, _L, _P, _L, _P, _L, _I, _I, _P, _L, _P, _P, _P, _L, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "fx_gated_group_norm": [_P, _P, _I, _L, _P, _I, _F, _I, _P, _I, _I, _I, _I, _P],
     "fx_prefill_attention": [_P, _L, _P, _P, _P, _I, _I, _P, _I, _P, _P, _L, _I, _I, _I, _I, _F, _P],
     "fx_prefill_attention_tc": [_P, _L, _I, _P, _P, _I, _P, _I, _I, _P, _I, _P, _P, _L, _I, _I, _I, _I, _F, _P, _P, _P,
                                 _P, _I, _P],
@@ -276,11 +284,101 @@ def rmsnorm(x, weight, eps, out, rows=None, stream=None):
     return out
 
 
-def silu_mul(gu, out, stream=None):
+GATE_ACTIVATIONS = {"silu": 0, "relu": 1}   # what a gated feed-forward passes its gate through
+
+
+def gate_code(activation: str) -> int:
+    try:
+        return GATE_ACTIVATIONS[activation]
+    except KeyError:
+        raise KernelError(f"gate activation {activation!r}: the kernels know {', '.join(GATE_ACTIVATIONS)}") from None
+
+
+def silu_mul(gu, out, stream=None, activation="silu"):
+    """out = act(gate) * up over rows of [gate | up]."""
     rows, n = out.shape
     if gu.shape[1] != 2 * n:
         raise KernelError("silu_mul expects [gate | up] rows of twice the output width")
-    call("fx_silu_mul", _ptr(gu), _rows(gu), _ptr(out), _rows(out), code(gu), None, rows, n,
+    call("fx_glu_mul", _ptr(gu), _rows(gu), _ptr(out), _rows(out), code(gu), None, rows, n, gate_code(activation),
+         stream if stream is not None else stream_ptr())
+    return out
+
+
+def layernorm(x, weight, eps, out, rows=None, stream=None):
+    """out = (x - mean) / sqrt(var + eps) * weight over rows of the 32-bit stream ``x`` (``out`` may be ``x``)."""
+    if x.dtype != torch.float32:
+        raise KernelError("layernorm reads the 32-bit residual stream")
+    call("fx_layernorm", _ptr(x), _ptr(rows), _ptr(weight), code(weight), float(eps), _ptr(out), code(out), out.shape[0],
+         x.shape[1], stream if stream is not None else stream_ptr())
+    return out
+
+
+def layernorm_residual(h, y, weight, eps, *, scale=1.0, y2=None, scale2=1.0, then=None, stream=None):
+    """h += ln(scale * y + scale2 * y2) * weight, the norm over whole rows.  ``then`` = (weight, eps, out): also
+    out = ln(new h) * weight, in the same kernel."""
+    T, H = h.shape
+    if h.dtype != torch.float32 or y.shape != h.shape or (y2 is not None and y2.shape != h.shape):
+        raise KernelError("layernorm_residual: the stream is 32-bit and the sublayer's output has its shape")
+    for t in (y, y2):
+        if t is not None and not t.is_contiguous():
+            raise KernelError("layernorm_residual takes contiguous rows")
+    wn, en, out = then if then is not None else (None, 0.0, None)
+    call("fx_layernorm_residual", _ptr(h), _ptr(y), code(y), float(scale), _ptr(y2), code(y2) if y2 is not None else 0,
+         float(scale2), _ptr(weight), code(weight), float(eps), _ptr(wn), code(wn) if wn is not None else 0, float(en),
+         _ptr(out), code(out) if out is not None else 0, T, H, stream if stream is not None else stream_ptr())
+    return out
+
+
+def scale_(x, factor, stream=None):
+    """x *= factor (32-bit, in place)."""
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise KernelError("scale_ takes a contiguous 32-bit tensor")
+    call("fx_scale", _ptr(x), x.numel(), float(factor), stream if stream is not None else stream_ptr())
+    return x
+
+
+def delta_prep(proj, conv_w, taps, tail, ba, a_log, dt_bias, token_seq, seq_slot, out, beta, g, G, D, H, V, stream=None):
+    """What the gated delta rule needs before its recurrence, from rows ``proj`` = [q | k | v | ...] as projected:
+    short causal convolution (``conv_w`` [channels, taps], the inputs before the step from ``tail`` [slots, taps-1,
+    channels]) and SiLU, q and k to unit length per head (q also times D^-1/2), into ``out`` [T, channels] 32-bit;
+    beta = sigmoid(b) and g = exp(-exp(A_log) softplus(a + dt_bias)) from ``ba`` = [b | a] 32-bit rows."""
+    T = proj.shape[0]
+    call("fx_delta_prep", _ptr(proj), code(proj), _rows(proj), _ptr(conv_w), code(conv_w), int(taps), _ptr(tail), _ptr(ba),
+         _rows(ba), _ptr(a_log), _ptr(dt_bias), _ptr(token_seq), _ptr(seq_slot), _ptr(out), _ptr(beta), _ptr(g), T, G, D, H, V,
+         stream if stream is not None else stream_ptr())
+
+
+def conv_tail_update(proj, channels, taps, tail, token_seq, seq_slot, n_entries, stream=None):
+    """The last ``taps - 1`` inputs of every entry of the step become its request's convolution tail."""
+    call("fx_conv_tail_update", _ptr(proj), code(proj), _rows(proj), int(channels), int(taps), _ptr(tail), _ptr(token_seq),
+         _ptr(seq_slot), proj.shape[0], int(n_entries), stream if stream is not None else stream_ptr())
+
+
+def state_scan(q, k, v, g, g_ld, beta, state, out, token_seq, seq_slot, n_entries, H, G, D, V, silu_on_load=False,
+               stream=None):
+    """The recurrence of a mixer with a matrix state per head, over every entry's tokens in order:
+    ``beta`` None:  S = g S + k v^T;  else  S = g S; u = beta (v - S^T k); S += k u^T;  then out = S^T q.
+    ``q``, ``k`` [T, G*D] and ``v`` [T, H*V] are row views (one element type); ``g`` is [T, H] with row stride
+    ``g_ld`` (0: one decay per head); ``state`` [slots, H, V, D] and ``out`` [T, H*V] are 32-bit."""
+    if q.dtype != k.dtype or q.dtype != v.dtype:
+        raise KernelError("state_scan: q, k and v share one element type")
+    if state.dtype != torch.float32 or out.dtype != torch.float32 or g.dtype != torch.float32:
+        raise KernelError("state_scan: state, decays and read-out are 32-bit")
+    T = q.shape[0]
+    call("fx_state_scan", _ptr(q), _rows(q), _ptr(k), _rows(k), _ptr(v), _rows(v), code(q), int(silu_on_load), _ptr(g),
+         int(g_ld), _ptr(beta), _ptr(state), _ptr(out), _rows(out), _ptr(token_seq), _ptr(seq_slot), T, int(n_entries),
+         H, G, D, V, stream if stream is not None else stream_ptr())
+    return out
+
+
+GROUP_NORM_GATES = {"silu": 0, "sigmoid": 1}
+
+
+def gated_group_norm(x, gate, weight, eps, gate_activation, out, groups, width, stream=None):
+    """out[t, g, :] = x[t, g, :] / sqrt(mean(x[t, g, :]^2) + eps) * weight * act(gate[t, g, :]); ``x`` 32-bit
+    [T, groups*width], ``gate`` a row view of the same width, ``weight`` [width]."""
+    call("fx_gated_group_norm", _ptr(x), _ptr(gate), code(gate), _rows(gate), _ptr(weight), code(weight), float(eps),
+         GROUP_NORM_GATES[gate_activation], _ptr(out), code(out), x.shape[0], int(groups), int(width),
          stream if stream is not None else stream_ptr())
     return out
 
@@ -362,13 +460,21 @@ def rope_kv_write(qkv, positions, token_seq, seq_slot, inv_freq, rotary_dim, k_p
 
 
 def paged_attention(q, k_pages, v_pages, block_table, page_size, positions, token_seq, seq_slot, out, n_heads,
-                    n_kv_heads, head_dim, window, scale, stream=None):
-    """``q`` is a [T, >= n_heads*head_dim] view whose rows start with the query heads."""
+                    n_kv_heads, head_dim, window, scale, stream=None, softcap=None):
+    """``q`` is a [T, >= n_heads*head_dim] view whose rows start with the query heads.  ``softcap`` c: scaled
+    scores pass through c * tanh(s / c) before the softmax."""
     T = q.shape[0]
     call("fx_paged_attention", _ptr(q), _rows(q), _ptr(k_pages), _ptr(v_pages), code(q), _ptr(block_table),
          block_table.shape[1], page_size, _ptr(positions), _ptr(token_seq), _ptr(seq_slot), _ptr(out), _rows(out), T,
-         n_heads, n_kv_heads, head_dim, int(window or 0), float(scale), stream if stream is not None else stream_ptr())
+         n_heads, n_kv_heads, head_dim, int(window or 0), float(scale), float(softcap or 0.0),
+         stream if stream is not None else stream_ptr())
     return out
+
+
+def softcap_ok(qkv, few_new_tokens: bool, head_dim: int, page_size: int) -> bool:
+    """Whether the kernel that would run these operands (split keys for few new tokens a request, tiles of queries
+    otherwise) takes a cap on the scores; if not, :func:`paged_attention` does."""
+    return False
 
 
 PREFILL_TILE = 64
@@ -784,21 +890,23 @@ def linear(x, w, out, *, bias=None, accumulate=False, status=None, stream=None, 
     return gemm(x, w, out, bias=bias, accumulate=accumulate, stream=stream)
 
 
-def gated_linear(x, w_gu, out, *, status=None, stream=None):
-    """out = silu(x . gate^T) * (x . up^T) with ``w_gu`` = [gate rows ; up rows]: picks the kernel as
-    :func:`linear` does; the gate|up intermediate reaches memory only on the CUDA-core path."""
+def gated_linear(x, w_gu, out, *, status=None, stream=None, activation="silu"):
+    """out = act(x . gate^T) * (x . up^T) with ``w_gu`` = [gate rows ; up rows] and act SiLU or ReLU
+    (``activation``): picks the kernel as :func:`linear` does; the gate|up intermediate reaches memory only on the
+    CUDA-core path."""
     T, I = out.shape
+    gated = 1 + gate_code(activation)     # the kernels' argument: 0 plain, 1 SiLU gate, 2 ReLU gate
     if T <= SKINNY_MAX_TOKENS and tc_ok(x, w_gu) and swap_better(T, 2 * I, x.shape[1]):
-        return gemm_tc_swap(x, w_gu, out, gated=True, status=status, stream=stream)
+        return gemm_tc_swap(x, w_gu, out, gated=gated, status=status, stream=stream)
     if T <= SKINNY_MAX_TOKENS and skinny_ok(x, w_gu):
-        return gemm_skinny(x, w_gu, out, gated=True, stream=stream)
+        return gemm_skinny(x, w_gu, out, gated=gated, stream=stream)
     if T > SKINNY_MAX_TOKENS and tc_ok(x, w_gu):
         if w_gu.dim() == 2 and pairs_better(T, I, gated=True):
-            return gemm_tc2(x, w_gu, out, gated=True, status=status, stream=stream)
-        return gemm_tc(x, w_gu, out, gated=True, status=status, stream=stream)
+            return gemm_tc2(x, w_gu, out, gated=gated, status=status, stream=stream)
+        return gemm_tc(x, w_gu, out, gated=gated, status=status, stream=stream)
     gu = torch.empty(T, 2 * I, dtype=out.dtype, device=out.device)
     gemm(x, w_gu, gu, stream=stream)
-    return silu_mul(gu, out, stream=stream)
+    return silu_mul(gu, out, stream=stream, activation=activation)
 
 
 def combine_norm_ok(h, y) -> bool:

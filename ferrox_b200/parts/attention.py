@@ -86,38 +86,42 @@ class GqaAttention(Mixer):
         self.q_size = s.n_heads * s.head_dim
         self.kv_size = s.n_kv_heads * s.head_dim
         self.scale = s.softmax_scale if s.softmax_scale is not None else 1.0 / math.sqrt(s.head_dim)
+        self.softcap = float(s.softcap) if s.softcap else None
+        if self.softcap is not None and self.softcap < 0:
+            raise ValueError(f"softcap={s.softcap}: the cap of the scores is positive")
+        names = dict(q="q_proj.weight", k="k_proj.weight", v="v_proj.weight", o="o_proj.weight",
+                     q_bias="q_proj.bias", k_bias="k_proj.bias", v_bias="v_proj.bias")
+        names.update(dict(s.tensor_names or ()))
+        self._names = {key: s.prefix + n for key, n in names.items()}
+        # tied values: the v rows of the fused product are the k rows once more, so that every kernel after it
+        # finds [q | k | v] rows as ever and the position part rotates the k copy only
+        self._qkv_keys = ("q", "k", "k") if s.tied_values else ("q", "k", "v")
 
     def cache_spec(self):
         return CacheSpec(paged=KvCacheSpec(self.spec.n_kv_heads, self.spec.head_dim, self.spec.window))
 
     def tensor_decls(self):
-        s, p = self.spec, self.spec.prefix
-        d = [
-            TensorDecl(p + "q_proj.weight", (self.q_size, s.hidden)),
-            TensorDecl(p + "k_proj.weight", (self.kv_size, s.hidden)),
-            TensorDecl(p + "v_proj.weight", (self.kv_size, s.hidden)),
-            TensorDecl(p + "o_proj.weight", (s.hidden, self.q_size)),
-        ]
+        s, n = self.spec, self._names
+        sizes = dict(q=self.q_size, k=self.kv_size, v=self.kv_size)
+        keys = sorted(set(self._qkv_keys))
+        d = [TensorDecl(n[key], (sizes[key], s.hidden)) for key in keys]
+        d.append(TensorDecl(n["o"], (s.hidden, self.q_size)))
         if s.qkv_bias:
-            d += [
-                TensorDecl(p + "q_proj.bias", (self.q_size,)),
-                TensorDecl(p + "k_proj.bias", (self.kv_size,)),
-                TensorDecl(p + "v_proj.bias", (self.kv_size,)),
-            ]
+            d += [TensorDecl(n[key + "_bias"], (sizes[key],)) for key in keys]
         return d
 
     def load(self, src, rt):
         super().load(src, rt)
-        p = self.spec.prefix
-        ws = [src.get(p + f"{n}_proj.weight") for n in "qkv"]
+        n = self._names
+        ws = [src.get(n[key]) for key in self._qkv_keys]
         dt = _common_dtype(ws)
         self.w_qkv = torch.cat([w.to(dt) for w in ws], dim=0).contiguous()
         self.b_qkv = None
         if self.spec.qkv_bias:
-            bs = [src.get(p + f"{n}_proj.bias") for n in "qkv"]
+            bs = [src.get(n[key + "_bias"]) for key in self._qkv_keys]
             bdt = _common_dtype(bs)
             self.b_qkv = torch.cat([b.to(bdt) for b in bs]).contiguous()
-        self.w_o = src.get(p + "o_proj.weight")
+        self.w_o = src.get(n["o"])
         self.position.load(src, rt)
         # zeroed scratch of the decode attention kernel that merges its own key ranges (it leaves it zeroed)
         self._range_counters = (torch.zeros(RANGE_COUNTERS, dtype=torch.int32, device=rt.device)
@@ -130,6 +134,11 @@ class GqaAttention(Mixer):
         self.position.reset_after_fault()
 
     def forward_add(self, x, h, batch, cache):
+        self.forward_into(x, h, batch, cache, accumulate=True)
+
+    def forward_into(self, x, out, batch, cache, accumulate=False):
+        """out (+)= Wo . attention: ``out`` is the residual stream (accumulate) or a 32-bit buffer of its shape."""
+        h = out
         s = self.spec
         T = x.shape[0]
         qkv = self.rt.empty(T, self.q_size + 2 * self.kv_size)
@@ -144,14 +153,26 @@ class GqaAttention(Mixer):
         if in_kernel is None:
             self.position.rotate_and_store(qkv, batch, cache, s.n_heads, s.n_kv_heads, s.head_dim)
         attn = self.rt.empty(T, self.q_size)
-        if batch.max_new <= DECODE_ATTENTION_MAX_NEW:
+        if self.softcap is not None and not ops.softcap_ok(qkv, batch.max_new <= DECODE_ATTENTION_MAX_NEW, s.head_dim,
+                                                           cache.page_size):
+            # capped scores, where the faster kernels do not take them: a warp per (token, head)
+            ops.paged_attention(
+                qkv, cache.k, cache.v, cache.block_table, cache.page_size, batch.positions, batch.token_seq,
+                batch.seq_slot, attn, s.n_heads, s.n_kv_heads, s.head_dim, s.window, self.scale, stream=batch.stream,
+                softcap=self.softcap,
+            )
+        elif batch.max_new <= DECODE_ATTENTION_MAX_NEW:
             # few query tokens: split each request's keys over many blocks
             group = s.n_heads // s.n_kv_heads
             per_sm = ops.decode_tma_blocks_per_sm(qkv.dtype, s.head_dim, cache.page_size)
             # blocks per token: the tensor-core kernels take 16 query heads of a kv head at a time, the CUDA-core one 8
             kv_blocks = s.n_kv_heads * -(-group // (16 if qkv.dtype == torch.bfloat16 else 8))
+            # the most keys a token reads: the context limit, or a window (with the 64-key blocks it straddles)
+            reach = cache.block_table.shape[1] * cache.page_size
+            if s.window is not None:
+                reach = min(reach, (s.window + 63) // 64 * 64 + 64)
             split_len, n_splits = ops.decode_split_plan(
-                T, kv_blocks, cache.block_table.shape[1] * cache.page_size, per_sm or 3, single_is_final=per_sm > 0,
+                T, kv_blocks, reach, per_sm or 3, single_is_final=per_sm > 0,
                 run_latency=ops.DECODE_RUN_LATENCY if per_sm else 0.0)
             part_acc = self.rt.empty(T, s.n_heads, n_splits, s.head_dim, dtype=torch.float32)
             part_ml = self.rt.empty(T, s.n_heads, n_splits, 2, dtype=torch.float32)
@@ -190,7 +211,8 @@ class GqaAttention(Mixer):
                 batch.seq_slot, attn, s.n_heads, s.n_kv_heads, s.head_dim, s.window, self.scale, stream=batch.stream,
             )
         # (the attention's last blocks only add up key ranges: the memory system is idle under them)
-        ops.linear(attn, self.w_o, h, accumulate=True, status=batch.status, stream=batch.stream, after_short_kernel=True)
+        ops.linear(attn, self.w_o, h, accumulate=accumulate, status=batch.status, stream=batch.stream,
+                   after_short_kernel=True)
 
 
 register_part("gqa_attention", GqaAttention, replace=True)

@@ -112,6 +112,11 @@ class Norm(Part):
         has just produced the rows can apply itself; None otherwise."""
         return None
 
+    def as_layer_norm(self):
+        """(weight, eps) if this norm is (x - mean) / sqrt(variance + eps) * weight over whole rows without a
+        bias; None otherwise."""
+        return None
+
 
 class Mixer(Part):
     def cache_spec(self):
@@ -119,6 +124,14 @@ class Mixer(Part):
 
     def forward_add(self, x, h, batch, cache) -> None:  # pragma: no cover - interface
         raise NotImplementedError
+
+    def forward_into(self, x, out, batch, cache, accumulate: bool = False) -> None:
+        """out (+)= mixer(x) into a 32-bit [tokens, hidden] buffer: what a block needs that norms the mixer's
+        output before it adds it.  Mixers whose last kernel can write instead of add override this; the default
+        clears ``out`` and adds."""
+        if not accumulate:
+            out.zero_()
+        self.forward_add(x, out, batch, cache)
 
 
 class FeedForward(Part):
@@ -129,6 +142,12 @@ class FeedForward(Part):
 
     def forward_add(self, x, h, batch) -> None:  # pragma: no cover - interface
         raise NotImplementedError
+
+    def forward_into(self, x, out, batch, accumulate: bool = False) -> None:
+        """out (+)= ffn(x) into a 32-bit [tokens, hidden] buffer (see :meth:`Mixer.forward_into`)."""
+        if not accumulate:
+            out.zero_()
+        self.forward_add(x, out, batch)
 
 
 class Block(Part):

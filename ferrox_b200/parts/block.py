@@ -8,6 +8,8 @@ whatever norm, mixer and feed-forward its spec names.
 """
 from __future__ import annotations
 
+import torch
+
 from ..kernels import ops
 from .base import Block, build_part, register_part
 
@@ -57,4 +59,93 @@ class PreNormBlock(Block):
         return None
 
 
+class SandwichNormBlock(Block):
+    """A norm before and after each sublayer,
+
+        h += post1(mixer(norm1(h)));   h += post2(ffn(norm2(h)))
+
+    (``ffn`` None: the layer ends after the mixer).  The sublayer's output is a 32-bit buffer; one kernel norms it,
+    adds it to the stream and, where the norm that comes next is a layer norm too, applies that to the new row as
+    well (the mixer's post-norm with norm2, the feed-forward's post-norm with the next block's norm1).  A mixer
+    that is a weighted sum of mixers hands its parts over, and the same kernel takes the sum."""
+
+    passes_norm = True
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.norm1 = build_part(spec.norm1)
+        self.mixer = build_part(spec.mixer)
+        self.post1 = build_part(spec.post1)
+        self.has_ffn = spec.ffn is not None
+        self.norm2 = build_part(spec.norm2) if self.has_ffn else None
+        self.ffn = build_part(spec.ffn) if self.has_ffn else None
+        self.post2 = build_part(spec.post2) if self.has_ffn else None
+
+    def _parts(self):
+        return [p for p in (self.norm1, self.mixer, self.post1, self.norm2, self.ffn, self.post2) if p is not None]
+
+    def tensor_decls(self):
+        return [d for p in self._parts() for d in p.tensor_decls()]
+
+    def load(self, src, rt):
+        super().load(src, rt)
+        for part in self._parts():
+            part.load(src, rt)
+
+    def reset_after_fault(self):
+        for part in self._parts():
+            part.reset_after_fault()
+
+    @property
+    def graph_safe(self):
+        return all(p.graph_safe for p in self._parts())
+
+    def _add_normed(self, h, outs, post, then_norm, batch):
+        """h += post(sum of scale * y over ``outs``); returns then_norm(h) if the same kernel made it, else None."""
+        ln = post.as_layer_norm()
+        nxt = then_norm.as_layer_norm() if then_norm is not None else None
+        if ln is not None and len(outs) <= 2:
+            (y, sc), (y2, sc2) = outs[0], (outs[1] if len(outs) == 2 else (None, 1.0))
+            then = None
+            if nxt is not None:
+                then = (nxt[0], nxt[1], self.rt.empty(h.shape[0], h.shape[1]))
+            return ops.layernorm_residual(h, y, ln[0], ln[1], scale=sc, y2=y2, scale2=sc2, then=then,
+                                          stream=batch.stream)
+        # any other norm: sum the parts, norm the sum as a stream of its own, add
+        total = outs[0][0]
+        if outs[0][1] != 1.0:
+            ops.scale_(total, outs[0][1], stream=batch.stream)
+        for y, sc in outs[1:]:
+            if sc != 1.0:
+                ops.scale_(y, sc, stream=batch.stream)
+            ops.residual_add(total, y, stream=batch.stream)
+        ops.residual_add(h, post.forward(total), stream=batch.stream)
+        return None
+
+    def forward(self, h, batch, cache, x=None, then_norm=None):
+        if x is None:
+            with ops.trace_scope("norm"):
+                x = self.norm1.forward(h)
+        with ops.trace_scope("mixer"):
+            if hasattr(self.mixer, "forward_parts"):
+                outs = self.mixer.forward_parts(x, batch, cache)
+            else:
+                y = self.rt.empty(h.shape[0], h.shape[1], dtype=torch.float32)
+                self.mixer.forward_into(x, y, batch, cache, accumulate=False)
+                outs = [(y, 1.0)]
+        with ops.trace_scope("norm"):
+            x2 = self._add_normed(h, outs, self.post1, self.norm2 if self.has_ffn else then_norm, batch)
+        if not self.has_ffn:
+            return x2
+        if x2 is None:
+            with ops.trace_scope("norm"):
+                x2 = self.norm2.forward(h)
+        with ops.trace_scope("feed-forward"):
+            y = self.rt.empty(h.shape[0], h.shape[1], dtype=torch.float32)
+            self.ffn.forward_into(x2, y, batch, accumulate=False)
+        with ops.trace_scope("norm"):
+            return self._add_normed(h, [(y, 1.0)], self.post2, then_norm, batch)
+
+
 register_part("pre_norm", PreNormBlock, replace=True)
+register_part("sandwich_norm", SandwichNormBlock, replace=True)

@@ -1,0 +1,157 @@
+"""Mixers that carry a matrix state per head from token to token instead of reading old keys.
+
+``gated_delta_rule``:  per head a state S [head_dim, value_dim];  for every token
+
+    S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q
+
+with q, k, v after a short causal convolution and SiLU, q and k of unit length (q times head_dim^-1/2),
+beta = sigmoid(Wb x), g = exp(-exp(A_log) softplus(Wa x + dt_bias)); each head's o is RMS-normed, weighted, and
+gated by SiLU(Wg x) before the output projection.  The convolution's last taps - 1 inputs are state as well.
+
+``decayed_linear_attention``:  S <- d_h S + k v^T, o = S^T q on SiLU(q, k, v) with one fixed decay per head; the
+heads' read-outs are RMS-normed together, weighted, and gated by sigmoid(Wg x).
+
+The states live in the cache manager's slots as 32-bit tensors; the recurrences, the gates and the norms are
+32-bit (``csrc/linear_state.cu``); the projections run in the engine's dtype.  Tokens of a request are taken in
+order whatever the step looks like, so a position's output does not depend on how the request was cut.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..cache.specs import CacheSpec, StateSpec
+from ..kernels import ops
+from ..weights.loader import TensorDecl
+from .base import Mixer, register_part
+
+
+def _cat_rows(tensors):
+    dt = torch.float32 if any(t.dtype == torch.float32 for t in tensors) else tensors[0].dtype
+    return torch.cat([t.to(dt) for t in tensors], dim=0).contiguous()
+
+
+class _StateMixer(Mixer):
+    graph_safe = True
+
+    def forward_add(self, x, h, batch, cache):
+        self.forward_into(x, h, batch, cache, accumulate=True)
+
+
+class GatedDeltaRule(_StateMixer):
+    def __init__(self, spec):
+        super().__init__(spec)
+        s = spec
+        if s.n_heads % s.n_kv_heads:
+            raise ValueError("n_heads must be a multiple of n_kv_heads")
+        if s.conv_taps < 1 or s.conv_taps > 16:
+            raise ValueError(f"conv_taps={s.conv_taps}: between 1 and 16")
+        if s.head_dim > 256:
+            raise ValueError(f"head_dim={s.head_dim}: the recurrence kernel holds at most 256 rows of a state column")
+        self.qk = s.n_kv_heads * s.head_dim
+        self.vv = s.n_heads * s.value_dim
+        self.channels = 2 * self.qk + self.vv
+
+    def cache_spec(self):
+        s = self.spec
+        return CacheSpec(state=StateSpec(parts=(
+            ("matrix", (s.n_heads, s.value_dim, s.head_dim)),           # S, column by column
+            ("conv_tail", (max(1, s.conv_taps - 1), self.channels)),    # the convolution's last inputs, oldest first
+        )))
+
+    def tensor_decls(self):
+        s, p = self.spec, self.spec.prefix
+        d = []
+        for n, rows in (("q", self.qk), ("k", self.qk), ("v", self.vv)):
+            d.append(TensorDecl(p + n, (rows, s.hidden)))
+            d.append(TensorDecl(p + n + ".conv", (rows, s.conv_taps)))
+        d += [
+            TensorDecl(p + "b", (s.n_heads, s.hidden)), TensorDecl(p + "a", (s.n_heads, s.hidden)),
+            TensorDecl(p + "A_log", (s.n_heads,), init="zeros"), TensorDecl(p + "dt_bias", (s.n_heads,), init="zeros"),
+            TensorDecl(p + "norm", (s.value_dim,), init="ones"),
+            TensorDecl(p + "g", (self.vv, s.hidden)), TensorDecl(p + "o", (s.hidden, self.vv)),
+        ]
+        return d
+
+    def load(self, src, rt):
+        super().load(src, rt)
+        p = self.spec.prefix
+        self.w_in = _cat_rows([src.get(p + n) for n in ("q", "k", "v", "g")])          # rows [q | k | v | gate]
+        self.w_ba = _cat_rows([src.get(p + "b"), src.get(p + "a")])                    # rows [b | a]
+        self.conv_w = torch.cat([src.get(p + n + ".conv").float() for n in ("q", "k", "v")], dim=0).contiguous()
+        self.a_log = src.get(p + "A_log").float().contiguous()
+        self.dt_bias = src.get(p + "dt_bias").float().contiguous()
+        self.norm_w = src.get(p + "norm").float().contiguous()
+        self.w_o = src.get(p + "o")
+
+    def forward_into(self, x, out, batch, cache, accumulate=False):
+        s, rt = self.spec, self.rt
+        T, H, G, D, V = x.shape[0], s.n_heads, s.n_kv_heads, s.head_dim, s.value_dim
+        f32 = torch.float32
+        proj = rt.empty(T, self.channels + self.vv)
+        ops.linear(x, self.w_in, proj, status=batch.status, stream=batch.stream)
+        ba = rt.empty(T, 2 * H, dtype=f32)                     # the gates' inputs stay 32-bit
+        ops.linear(x, self.w_ba, ba, status=batch.status, stream=batch.stream)
+        qkv = rt.empty(T, self.channels, dtype=f32)
+        beta, g = rt.empty(T, H, dtype=f32), rt.empty(T, H, dtype=f32)
+        tail, state = cache.states["conv_tail"], cache.states["matrix"]
+        ops.delta_prep(proj, self.conv_w, s.conv_taps, tail, ba, self.a_log, self.dt_bias, batch.token_seq,
+                       batch.seq_slot, qkv, beta, g, G, D, H, V, stream=batch.stream)
+        ops.conv_tail_update(proj, self.channels, s.conv_taps, tail, batch.token_seq, batch.seq_slot, batch.n_seqs,
+                             stream=batch.stream)
+        read = rt.empty(T, self.vv, dtype=f32)
+        ops.state_scan(qkv[:, :self.qk], qkv[:, self.qk:2 * self.qk], qkv[:, 2 * self.qk:], g, H, beta, state, read,
+                       batch.token_seq, batch.seq_slot, batch.n_seqs, H, G, D, V, stream=batch.stream)
+        y = rt.empty(T, self.vv)
+        ops.gated_group_norm(read, proj[:, self.channels:], self.norm_w, s.norm_eps, "silu", y, H, V, stream=batch.stream)
+        ops.linear(y, self.w_o, out, accumulate=accumulate, status=batch.status, stream=batch.stream)
+
+
+class DecayedLinearAttention(_StateMixer):
+    def __init__(self, spec):
+        super().__init__(spec)
+        s = spec
+        if len(s.decay) != s.n_heads:
+            raise ValueError(f"decay lists {len(s.decay)} values for {s.n_heads} heads")
+        if s.head_dim > 256:
+            raise ValueError(f"head_dim={s.head_dim}: the recurrence kernel holds at most 256 rows of a state column")
+        self.qk = s.n_heads * s.head_dim
+        self.vv = s.n_heads * s.value_dim
+
+    def cache_spec(self):
+        s = self.spec
+        return CacheSpec(state=StateSpec(parts=(("matrix", (s.n_heads, s.value_dim, s.head_dim)),)))
+
+    def tensor_decls(self):
+        s, p = self.spec, self.spec.prefix
+        return [
+            TensorDecl(p + "q", (self.qk, s.hidden)), TensorDecl(p + "k", (self.qk, s.hidden)),
+            TensorDecl(p + "v", (self.vv, s.hidden)), TensorDecl(p + "g", (self.vv, s.hidden)),
+            TensorDecl(p + "o", (s.hidden, self.vv)), TensorDecl(p + "norm", (self.vv,), init="ones"),
+        ]
+
+    def load(self, src, rt):
+        super().load(src, rt)
+        p = self.spec.prefix
+        self.w_in = _cat_rows([src.get(p + n) for n in ("q", "k", "v", "g")])          # rows [q | k | v | gate]
+        self.norm_w = src.get(p + "norm").float().contiguous()
+        self.w_o = src.get(p + "o")
+        self.decay = torch.tensor([float(d) for d in self.spec.decay], dtype=torch.float32, device=rt.device)
+
+    def forward_into(self, x, out, batch, cache, accumulate=False):
+        s, rt = self.spec, self.rt
+        T, H, D, V = x.shape[0], s.n_heads, s.head_dim, s.value_dim
+        proj = rt.empty(T, 2 * self.qk + 2 * self.vv)
+        ops.linear(x, self.w_in, proj, status=batch.status, stream=batch.stream)
+        read = rt.empty(T, self.vv, dtype=torch.float32)
+        # SiLU of q, k, v where the recurrence reads them
+        ops.state_scan(proj[:, :self.qk], proj[:, self.qk:2 * self.qk], proj[:, 2 * self.qk:2 * self.qk + self.vv],
+                       self.decay, 0, None, cache.states["matrix"], read, batch.token_seq, batch.seq_slot, batch.n_seqs,
+                       H, H, D, V, silu_on_load=True, stream=batch.stream)
+        y = rt.empty(T, self.vv)
+        ops.gated_group_norm(read, proj[:, 2 * self.qk + self.vv:], self.norm_w, s.norm_eps, "sigmoid", y, 1, self.vv,
+                             stream=batch.stream)
+        ops.linear(y, self.w_o, out, accumulate=accumulate, status=batch.status, stream=batch.stream)
+
+
+register_part("gated_delta_rule", GatedDeltaRule, replace=True)
+register_part("decayed_linear_attention", DecayedLinearAttention, replace=True)

@@ -16,26 +16,39 @@ def pack_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
 
 
 class SwigluMlp(FeedForward):
+    """down( act(gate x) * (up x) ); ``spec.activation`` names act (SiLU unless the spec says ReLU)."""
+
     graph_safe = True
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.activation = getattr(spec, "activation", "silu")
+        ops.gate_code(self.activation)   # an unknown activation fails here, by name
+        names = getattr(spec, "tensor_names", None) or ("gate_proj.weight", "up_proj.weight", "down_proj.weight")
+        self._gate, self._up, self._down = (spec.prefix + n for n in names)
+
     def tensor_decls(self):
-        s, p = self.spec, self.spec.prefix
+        s = self.spec
         return [
-            TensorDecl(p + "gate_proj.weight", (s.intermediate, s.hidden)),
-            TensorDecl(p + "up_proj.weight", (s.intermediate, s.hidden)),
-            TensorDecl(p + "down_proj.weight", (s.hidden, s.intermediate)),
+            TensorDecl(self._gate, (s.intermediate, s.hidden)),
+            TensorDecl(self._up, (s.intermediate, s.hidden)),
+            TensorDecl(self._down, (s.hidden, s.intermediate)),
         ]
 
     def load(self, src, rt):
         super().load(src, rt)
-        p = self.spec.prefix
-        self.w_gu = pack_gate_up(src.get(p + "gate_proj.weight"), src.get(p + "up_proj.weight"))
-        self.w_down = src.get(p + "down_proj.weight")
+        self.w_gu = pack_gate_up(src.get(self._gate), src.get(self._up))
+        self.w_down = src.get(self._down)
 
     def forward_add(self, x, h, batch):
+        self.forward_into(x, h, batch, accumulate=True)
+
+    def forward_into(self, x, out, batch, accumulate=False):
         T, I = x.shape[0], self.spec.intermediate
         act = self.rt.empty(T, I)
-        ops.gated_linear(x, self.w_gu, act, status=batch.status, stream=batch.stream)  # silu(gate) * up in the epilogue
-        ops.linear(act, self.w_down, h, accumulate=True, status=batch.status, stream=batch.stream)
+        # act(gate) * up in the epilogue
+        ops.gated_linear(x, self.w_gu, act, status=batch.status, stream=batch.stream, activation=self.activation)
+        ops.linear(act, self.w_down, out, accumulate=accumulate, status=batch.status, stream=batch.stream)
 
 
 register_part("swiglu_mlp", SwigluMlp, replace=True)

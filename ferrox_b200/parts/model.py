@@ -22,6 +22,9 @@ class DecoderModel(Part):
         super().__init__(spec)
         self.layers = [build_part(b) for b in spec.layers]
         self.final_norm = build_part(spec.final_norm)
+        self.embedding_norm = build_part(spec.embedding_norm) if spec.embedding_norm is not None else None
+        if self.embedding_norm is not None and not hasattr(self.embedding_norm, "forward_in_place"):
+            raise ValueError("the embedding's norm must be able to norm the 32-bit stream in place")
         for e in spec.schedule:
             if not 0 <= e.layer < len(self.layers):
                 raise ValueError(f"schedule names layer {e.layer}, the model has {len(self.layers)}")
@@ -45,6 +48,8 @@ class DecoderModel(Part):
     def tensor_decls(self) -> List[TensorDecl]:
         s = self.spec
         d = [TensorDecl(s.embedding_name, (s.vocab_size, s.hidden))]
+        if self.embedding_norm is not None:
+            d += self.embedding_norm.tensor_decls()
         for layer in self.layers:
             d += layer.tensor_decls()
         d += self.final_norm.tensor_decls()
@@ -59,6 +64,8 @@ class DecoderModel(Part):
         for layer in self.layers:
             layer.load(src, rt)
         self.final_norm.load(src, rt)
+        if self.embedding_norm is not None:
+            self.embedding_norm.load(src, rt)
         self.head = self.embedding if s.head_name is None else src.get(s.head_name)
 
     def reset_after_fault(self) -> None:
@@ -67,7 +74,8 @@ class DecoderModel(Part):
         self.final_norm.reset_after_fault()
 
     def graph_safe(self) -> bool:
-        return all(l.graph_safe for l in self.layers) and self.final_norm.graph_safe
+        return (all(l.graph_safe for l in self.layers) and self.final_norm.graph_safe
+                and (self.embedding_norm is None or self.embedding_norm.graph_safe))
 
     def weight_bytes(self) -> int:
         seen, total = set(), 0
@@ -94,6 +102,8 @@ class DecoderModel(Part):
         h = rt.empty(batch.n_tokens, s.hidden, dtype=torch.float32)
         with ops.trace_scope("embedding"):
             ops.embed(self.embedding, batch.token_ids, h, status=batch.status, stream=batch.stream)
+            if self.embedding_norm is not None:
+                self.embedding_norm.forward_in_place(h)
         x = None    # the next block's first norm of h, when the block before it has computed it
         for i, entry in enumerate(s.schedule):
             block = self.layers[entry.layer]
@@ -110,4 +120,6 @@ class DecoderModel(Part):
             x = self.final_norm.forward(h, rows=batch.want_rows)
             logits = rt.empty(batch.n_want, s.vocab_size, dtype=torch.float32, fresh=True)   # the caller's
             ops.linear(x, self.head, logits, status=batch.status, stream=batch.stream)
+            if s.logit_scale != 1.0:
+                ops.scale_(logits, s.logit_scale, stream=batch.stream)
         return logits

@@ -26,4 +26,31 @@ class RmsNorm(Norm):
         return self.weight, self.spec.eps
 
 
+class LayerNorm(Norm):
+    """(x - mean) / sqrt(variance + eps) * w, the variance being the mean of the squared deviations; a weight and
+    no bias; statistics in 32 bits."""
+
+    graph_safe = True
+
+    def tensor_decls(self):
+        return [TensorDecl(self.spec.name, (self.spec.size,), init="ones")]
+
+    def load(self, src, rt):
+        super().load(src, rt)
+        self.weight = src.get(self.spec.name)
+
+    def forward(self, h, rows=None):
+        n = h.shape[0] if rows is None else rows.numel()
+        out = self.rt.empty(n, self.spec.size)
+        return ops.layernorm(h, self.weight, self.spec.eps, out, rows=rows)
+
+    def forward_in_place(self, h):
+        """The 32-bit stream normed where it lies."""
+        return ops.layernorm(h, self.weight, self.spec.eps, h)
+
+    def as_layer_norm(self):
+        return self.weight, self.spec.eps
+
+
 register_part("rms_norm", RmsNorm, replace=True)
+register_part("layer_norm", LayerNorm, replace=True)

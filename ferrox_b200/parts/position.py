@@ -83,6 +83,18 @@ class RopeNeox(RotaryEncoding):
     pairing = ops.PAIR_HALVES
 
 
+class RopeAdjacent(RotaryEncoding):
+    """Pairs of neighbours (2i, 2i + 1) of the first ``rotary_dim`` elements, pair i at theta^(-2i / rotary_dim);
+    the frequencies are worked out in 64 bits and rounded once."""
+
+    pairing = ops.PAIR_ADJACENT
+
+    def frequencies(self):
+        r = self.spec.rotary_dim
+        i = torch.arange(0, r // 2, dtype=torch.float64)
+        return torch.pow(torch.tensor(float(self.spec.theta), dtype=torch.float64), -2.0 * i / float(r)).to(torch.float32)
+
+
 class NoPosition(PositionEncoding):
     """No position encoding: keys and queries are stored as projected."""
 
@@ -101,3 +113,4 @@ class NoPosition(PositionEncoding):
 
 register_part("rope_neox", RopeNeox, replace=True)
 register_part("no_position", NoPosition, replace=True)
+register_part("rope_adjacent", RopeAdjacent, replace=True)

@@ -27,12 +27,32 @@ class NormSpec:
 
 
 @dataclass(frozen=True)
+class LayerNormSpec:
+    """(x - mean) / sqrt(variance + eps) * w over whole rows; a weight and no bias."""
+
+    size: int
+    eps: float
+    name: str  # the weight tensor's full name
+    kind: str = "layer_norm"
+
+
+@dataclass(frozen=True)
 class PositionSpec:
     """Rotary position encoding, split-half pairing (i, i + rotary_dim/2)."""
 
     rotary_dim: int
     theta: float
     kind: str = "rope_neox"
+
+
+@dataclass(frozen=True)
+class AdjacentRotarySpec:
+    """Rotary position encoding on pairs of neighbours (2i, 2i + 1) of the first ``rotary_dim`` elements of a
+    head, pair i at frequency theta^(-2i / rotary_dim); the rest of the head passes unchanged."""
+
+    rotary_dim: int
+    theta: float
+    kind: str = "rope_adjacent"
 
 
 @dataclass(frozen=True)
@@ -53,7 +73,53 @@ class AttentionSpec:
     window: Optional[int]  # None = all earlier keys; W = the last W positions, the query's own included
     prefix: str  # tensors: <prefix>{q,k,v}_proj.{weight,bias}, <prefix>o_proj.weight
     softmax_scale: Optional[float] = None  # None = 1/sqrt(head_dim)
+    softcap: Optional[float] = None  # c: the scaled scores pass through c * tanh(s / c) before the softmax
+    tied_values: bool = False  # the values are the keys as projected (before the position encoding); no v tensor
+    # names of the tensors after <prefix>, for checkpoints that spell them differently: keys q, k, v, o (weights)
+    # and q_bias, k_bias, v_bias
+    tensor_names: Optional[Tuple[Tuple[str, str], ...]] = None
     kind: str = "gqa_attention"
+
+
+@dataclass(frozen=True)
+class GatedDeltaSpec:
+    """Gated delta rule: a [head_dim, value_dim] state per head, short causal convolutions on q, k and v.
+    Tensors: <prefix>{q,k,v}, <prefix>{q,k,v}.conv [channels, taps], <prefix>b, <prefix>a, <prefix>A_log,
+    <prefix>dt_bias, <prefix>g, <prefix>norm [value_dim], <prefix>o."""
+
+    hidden: int
+    n_heads: int
+    n_kv_heads: int  # heads of q and k; value head h reads q/k head h // (n_heads / n_kv_heads)
+    head_dim: int
+    value_dim: int
+    conv_taps: int
+    norm_eps: float
+    prefix: str
+    kind: str = "gated_delta_rule"
+
+
+@dataclass(frozen=True)
+class DecayedLinearAttentionSpec:
+    """Linear attention with one fixed decay per head: S = d S + k v^T, o = S^T q on SiLU(q, k, v); the heads'
+    read-outs are RMS-normed together and gated by a sigmoid.  Tensors: <prefix>{q,k,v,g,o}, <prefix>norm."""
+
+    hidden: int
+    n_heads: int
+    head_dim: int
+    value_dim: int
+    decay: Tuple[float, ...]
+    norm_eps: float
+    prefix: str
+    kind: str = "decayed_linear_attention"
+
+
+@dataclass(frozen=True)
+class MixerSumSpec:
+    """Several mixers read the same input; the result is sum_i scales[i] * mixers[i](x)."""
+
+    mixers: Tuple[object, ...]
+    scales: Tuple[float, ...]
+    kind: str = "mixer_sum"
 
 
 @dataclass(frozen=True)
@@ -62,6 +128,8 @@ class DenseMlpSpec:
     intermediate: int
     prefix: str  # tensors: <prefix>{gate,up,down}_proj.weight
     kind: str = "swiglu_mlp"
+    activation: str = "silu"  # what the gate passes through: silu or relu
+    tensor_names: Optional[Tuple[str, str, str]] = None  # (gate, up, down) after <prefix>, if spelled differently
 
 
 @dataclass(frozen=True)
@@ -90,6 +158,20 @@ class BlockSpec:
 
 
 @dataclass(frozen=True)
+class SandwichBlockSpec:
+    """A norm before and after each sublayer: h += post1(mixer(norm1(h))); h += post2(ffn(norm2(h))).
+    ``ffn`` None: the layer has no feed-forward (and no norm2 / post2)."""
+
+    norm1: object
+    mixer: object
+    post1: object
+    norm2: Optional[object]
+    ffn: Optional[object]
+    post2: Optional[object]
+    kind: str = "sandwich_norm"
+
+
+@dataclass(frozen=True)
 class ScheduleEntry:
     """One call in the order of execution: run ``layer`` against cache ``cache``.
 
@@ -114,6 +196,8 @@ class ModelSpec:
     embedding_name: str = "model.embed_tokens.weight"
     head_name: Optional[str] = "lm_head.weight"  # None = tied to the embedding
     eos_token_ids: Tuple[int, ...] = field(default_factory=tuple)
+    embedding_norm: Optional[object] = None  # a norm applied to the embedding rows (the stream stays 32-bit)
+    logit_scale: float = 1.0  # the head's output is multiplied by this
 
     @property
     def n_caches(self) -> int:
