@@ -66,7 +66,7 @@ class GatedDeltaRule(_StateMixer):
             d.append(TensorDecl(p + n + ".conv", (rows, s.conv_taps)))
         d += [
             TensorDecl(p + "b", (s.n_heads, s.hidden)), TensorDecl(p + "a", (s.n_heads, s.hidden)),
-            TensorDecl(p + "A_log", (s.n_heads,), init="zeros"), TensorDecl(p + "dt_bias", (s.n_heads,), init="zeros"),
+            TensorDecl(p + "A_log", (s.n_heads,)), TensorDecl(p + "dt_bias", (s.n_heads,)),
             TensorDecl(p + "norm", (s.value_dim,), init="ones"),
             TensorDecl(p + "g", (self.vv, s.hidden)), TensorDecl(p + "o", (s.hidden, self.vv)),
         ]

@@ -1,0 +1,61 @@
+"""Tiny Safepel configurations that differ from each other in every size, constant and in the order of layers, and
+the helper that writes a folder of random weights for one (into a temporary folder, never committed)."""
+from __future__ import annotations
+
+ARCH = "Safepel"
+
+
+def delta(heads, kv_heads, dim, vdim, conv, ff):
+    return {"type": "delta", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": conv},
+            "mlp": None if ff is None else {"kind": "dense", "ff": ff}}
+
+
+def parallel(heads, kv_heads, dim, window, rot_dims, base, scale, softcap, rheads, rdim, rvdim, decay, ls, rs, ff):
+    return {"type": "parallel", "mlp": None if ff is None else {"kind": "dense", "ff": ff}, "mixer": {
+        "left": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "mask": {"size": window},
+                 "rot": {"dims": rot_dims, "base": base}, "scale": scale, "softcap": softcap},
+        "right": {"heads": rheads, "dim": rdim, "vdim": rvdim, "decay": decay},
+        "left_scale": ls, "right_scale": rs}}
+
+
+# A: delta first, alternating; grouped q/k heads; window shorter than a page; rotary on half of the head.
+SAFEPEL_A = {
+    "architecture": ARCH, "vocab": 211, "width": 64, "norm": {"eps": 1e-5}, "logit_scale": 0.5,
+    "layers": [
+        delta(4, 2, 16, 24, 4, 96),
+        parallel(4, 2, 32, 7, 16, 10000.0, 0.25, 8.0, 3, 16, 24, [0.5, 0.9, 0.995], 0.7, 1.3, 96),
+        delta(4, 2, 16, 24, 4, 96),
+    ],
+}
+
+# B: parallel first, two of the same type in a row, a layer without feed-forward, sizes that are no power of two and
+# no multiple of 16, one q/k head for all, taps 2, a window that crosses pages, full rotary, scales of 1.
+SAFEPEL_B = {
+    "architecture": ARCH, "vocab": 97, "width": 80, "norm": {"eps": 3e-6}, "logit_scale": 2.0,
+    "layers": [
+        parallel(6, 3, 24, 21, 24, 500.0, 0.3, 3.0, 2, 20, 12, [0.8, 0.97], 1.0, 1.0, None),
+        parallel(2, 1, 48, 40, 32, 1000000.0, 0.11, 30.0, 5, 8, 40, [0.3, 0.6, 0.9, 0.99, 0.999], 1.5, 0.4, 56),
+        delta(3, 1, 20, 12, 2, 120),
+        delta(2, 2, 40, 36, 3, None),
+    ],
+}
+
+# C: one layer of each type with heads == kv_heads, a window of one (a token sees itself only), no rotation, taps 1.
+SAFEPEL_C = {
+    "architecture": ARCH, "vocab": 50, "width": 32, "norm": {"eps": 1e-6}, "logit_scale": 1.0,
+    "layers": [
+        parallel(2, 2, 16, 1, 0, 10000.0, 0.5, 5.0, 1, 8, 8, [0.9], 1.0, 2.0, 48),
+        delta(2, 2, 8, 8, 1, 48),
+    ],
+}
+
+CONFIGS = {"A": (SAFEPEL_A, 11), "B": (SAFEPEL_B, 12), "C": (SAFEPEL_C, 13)}
+
+
+def make_folder(tmp_path, name, std=0.15):
+    from ferrox_b200 import write_random_model
+
+    cfg, seed = CONFIGS[name]
+    folder = str(tmp_path / f"safepel_{name}")
+    write_random_model(folder, cfg, seed, dtype="bfloat16", std=std, norm_init="around_one")
+    return folder

@@ -1,0 +1,421 @@
+"""The engine's Safepel model against the plain implementation: every mechanism alone, then whole models under every
+way of cutting the work (whole prompts, a decoded tail, portions down to two tokens, mixed batches with pages and
+slots used again, long decoding, generation through the scheduler), in 32-bit and in bfloat16, on configurations
+that differ in every size, constant and in the order of layers."""
+import random
+
+import pytest
+import torch
+
+import plain_safepel as ps
+import replay_util as ru
+from safepel_configs import CONFIGS, SAFEPEL_A, SAFEPEL_B, make_folder
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = {"float32": (torch.float32, 5e-5), "bfloat16": (torch.bfloat16, 3e-2)}
+
+
+def rel(got, want):
+    return float((got.float().cpu() - want.float().cpu()).abs().max() / want.float().abs().max().clamp_min(1e-30))
+
+
+def load_part(spec, tensors, dtype):
+    from ferrox_b200.parts import build  # noqa: F401  (registers the built-in parts)
+    from ferrox_b200.parts.base import Runtime, build_part
+    from ferrox_b200.weights import loader as wl
+
+    part = build_part(spec)
+    rt = Runtime(torch.device(DEV), dtype)
+    part.load(wl.from_dict(tensors, part.tensor_decls(), DEV, dtype), rt)
+    return part, rt
+
+
+def random_tensors(part_spec, seed=0, std=0.1):
+    from ferrox_b200.parts import build  # noqa: F401
+    from ferrox_b200.parts.base import build_part
+    from ferrox_b200.weights.random_init import random_tensors as rt
+
+    return dict(rt(build_part(part_spec).tensor_decls(), seed, torch.bfloat16, std, "around_one"))
+
+
+class MixerHarness:
+    """Steps one mixer alone: a cache manager made from the mixer's own cache needs, the engine's batch."""
+
+    def __init__(self, part, rt, hidden, page_size=4, n_pages=64, max_slots=3, max_positions=512):
+        from ferrox_b200.cache.manager import CacheManager
+
+        self.part, self.rt, self.hidden = part, rt, hidden
+        self.mgr = CacheManager([part.cache_spec()], page_size=page_size, n_pages=n_pages, max_slots=max_slots,
+                                max_positions=max_positions, device=DEV, dtype=rt.dtype)
+        self.status = torch.zeros(1, dtype=torch.int32, device=DEV)
+
+    def step(self, portions):
+        """``portions``: [(slot, x rows [n, hidden])]; returns the mixer's output rows, in order."""
+        from ferrox_b200.engine.batch import StepEntry, flatten
+        from ferrox_b200.kernels import ops
+
+        entries = [StepEntry(slot, [0] * x.shape[0]) for slot, x in portions]
+        starts = self.mgr.reserve_step([e.slot for e in entries], [len(e.tokens) for e in entries])
+        assert starts is not None
+        for e, st in zip(entries, starts):
+            e.start = st
+        self.mgr.sync_tables()
+        batch = flatten(entries, torch.device(DEV), self.status, ops.stream_ptr())
+        x = torch.cat([x for _, x in portions]).to(DEV).to(self.rt.dtype).contiguous()
+        out = torch.full((x.shape[0], self.hidden), float("nan"), dtype=torch.float32, device=DEV)
+        self.part.forward_into(x, out, batch, self.mgr.layer_cache(0), accumulate=False)
+        self.mgr.commit_step([e.slot for e in entries], [len(e.tokens) for e in entries])
+        assert int(self.status.item()) == 0
+        return out.cpu()
+
+
+def run_in_cuts(harness, xs, cuts):
+    """Two requests' rows fed in the given cuts ([(n_a, n_b), ...]; 0: the request sits the step out); returns each
+    request's output rows."""
+    slots = [harness.mgr.open_request() for _ in xs]
+    at = [0] * len(xs)
+    outs = [[] for _ in xs]
+    for cut in cuts:
+        portions, who = [], []
+        for i, n in enumerate(cut):
+            n = min(n, xs[i].shape[0] - at[i])
+            if n > 0:
+                portions.append((slots[i], xs[i][at[i]:at[i] + n]))
+                who.append((i, n))
+                at[i] += n
+        if not portions:
+            continue
+        out = harness.step(portions)
+        r = 0
+        for i, n in who:
+            outs[i].append(out[r:r + n])
+            r += n
+    assert all(at[i] == xs[i].shape[0] for i in range(len(xs)))
+    for s in slots:
+        harness.mgr.close_request(s)
+    return [torch.cat(o) for o in outs]
+
+
+CUTS = {
+    "whole": [(10 ** 6, 0), (0, 10 ** 6)],
+    "one by one": [(1, 1)] * 400,
+    "portions": [(2, 3), (5, 2), (1, 7), (11, 2), (2, 1), (16, 33), (3, 2)] * 12,
+    "prompt then decode": [(40, 0), (1, 37)] + [(1, 1)] * 400,
+}
+
+
+# ------------------------------------------------------------------ mechanisms alone
+@pytest.mark.parametrize("dtype", list(DTYPES))
+def test_layer_norm_alone_and_with_the_residual_addition(dtype):
+    from ferrox_b200.kernels import ops
+    from ferrox_b200.parts.specs import LayerNormSpec
+
+    dt, tol = DTYPES[dtype]
+    g = torch.Generator().manual_seed(0)
+    for H in (80, 300):
+        spec = LayerNormSpec(size=H, eps=3e-6, name="n")
+        w = random_tensors(spec, std=0.3)
+        part, rt = load_part(spec, w, dt)
+        h = torch.randn(7, H, generator=g) * 4 + 2.5
+        want = ps.layer_norm(h, w["n"].float(), 3e-6)
+        got = part.forward(h.to(DEV))
+        assert got.dtype == dt and rel(got, want) < tol
+        rows = torch.tensor([6, 1], dtype=torch.int32, device=DEV)
+        assert torch.equal(part.forward(h.to(DEV), rows=rows), got[[6, 1]])
+        hd = h.to(DEV)
+        part.forward_in_place(hd)
+        assert rel(hd, want) < 3e-6
+        # h += ln(s1 y1 + s2 y2) w;  x = ln(h) w_next
+        y1, y2 = torch.randn(7, H, generator=g) * 3, torch.randn(7, H, generator=g)
+        w2 = (1 + 0.3 * torch.randn(H, generator=g)).to(torch.bfloat16)
+        hd = h.to(DEV)
+        x = torch.empty(7, H, dtype=dt, device=DEV)
+        ops.layernorm_residual(hd, y1.to(DEV), part.weight, 3e-6, scale=0.7, y2=y2.to(dt).to(DEV), scale2=1.3,
+                               then=(w2.to(DEV), 1e-5, x))
+        new_h = h + ps.layer_norm(0.7 * y1 + 1.3 * y2.to(dt).float(), w["n"].float(), 3e-6)
+        assert rel(hd, new_h) < 3e-6
+        assert rel(x, ps.layer_norm(new_h, w2.float(), 1e-5)) < tol
+        hd = h.to(DEV)
+        ops.layernorm_residual(hd, y1.to(DEV), part.weight, 3e-6)
+        assert rel(hd, h + ps.layer_norm(y1, w["n"].float(), 3e-6)) < 3e-6
+
+
+@pytest.mark.parametrize("dtype", list(DTYPES))
+def test_relu_gated_feed_forward_alone(dtype):
+    from types import SimpleNamespace
+
+    from ferrox_b200.kernels import ops
+    from ferrox_b200.parts.specs import DenseMlpSpec
+
+    dt, tol = DTYPES[dtype]
+    for hidden, ff in ((96, 160), (80, 56)):
+        spec = DenseMlpSpec(hidden=hidden, intermediate=ff, prefix="m.", activation="relu", tensor_names=("gate", "up", "down"))
+        w = random_tensors(spec)
+        part, rt = load_part(spec, w, dt)
+        wf = {k: v.float() for k, v in w.items()}
+        for T in (3, 70, 300):  # the decode-sized and the prompt-sized kernels
+            x = torch.randn(T, hidden, generator=torch.Generator().manual_seed(T)).to(dt)
+            out = torch.full((T, hidden), float("nan"), device=DEV)
+            part.forward_into(x.to(DEV), out, SimpleNamespace(status=None, stream=ops.stream_ptr()), accumulate=False)
+            assert rel(out, ps.feed_forward(x.float(), wf, "m.")) < tol
+
+
+@pytest.mark.parametrize("cut", list(CUTS))
+@pytest.mark.parametrize("dtype", list(DTYPES))
+def test_gated_delta_rule_alone(dtype, cut):
+    from ferrox_b200.parts.specs import GatedDeltaSpec
+
+    dt, tol = DTYPES[dtype]
+    for (H, G, D, V, taps, hidden) in ((4, 2, 16, 24, 4, 64), (3, 1, 20, 12, 2, 80), (2, 2, 72, 40, 3, 48)):
+        spec = GatedDeltaSpec(hidden=hidden, n_heads=H, n_kv_heads=G, head_dim=D, value_dim=V, conv_taps=taps,
+                              norm_eps=2e-6, prefix="d.")
+        w = random_tensors(spec, seed=H, std=0.3)
+        part, rt = load_part(spec, w, dt)
+        g = torch.Generator().manual_seed(5)
+        xs = [torch.randn(n, hidden, generator=g).to(dt).float() for n in (93, 61)]
+        m = dict(heads=H, kv_heads=G, dim=D, vdim=V)
+        wf = {k: v.float() for k, v in w.items()}
+        want = [ps.delta_mixer(x, wf, "d.", m, 2e-6) for x in xs]
+        got = run_in_cuts(MixerHarness(part, rt, hidden), xs, CUTS[cut])
+        for a, b in zip(got, want):
+            assert rel(a, b) < tol
+
+
+@pytest.mark.parametrize("cut", list(CUTS))
+@pytest.mark.parametrize("dtype", list(DTYPES))
+def test_decayed_linear_attention_alone_keeps_an_early_token(dtype, cut):
+    """One early token is made large: with a decay near 1 it must still be read hundreds of tokens later, and with a
+    fast decay it must be gone."""
+    from ferrox_b200.parts.specs import DecayedLinearAttentionSpec
+
+    dt, tol = DTYPES[dtype]
+    hidden = 64
+    spec = DecayedLinearAttentionSpec(hidden=hidden, n_heads=3, head_dim=16, value_dim=24, decay=(0.5, 0.97, 0.9995),
+                                      norm_eps=1e-5, prefix="r.")
+    w = random_tensors(spec, seed=2, std=0.3)
+    part, rt = load_part(spec, w, dt)
+    g = torch.Generator().manual_seed(6)
+    xs = [torch.randn(n, hidden, generator=g) for n in (330, 47)]
+    xs[0][2] *= 30.0
+    xs = [x.to(dt).float() for x in xs]
+    wf = {k: v.float() for k, v in w.items()}
+    m = dict(heads=3, dim=16, vdim=24, decay=[0.5, 0.97, 0.9995])
+    want = [ps.decayed_linear_attention(x, wf, "r.", m, 1e-5) for x in xs]
+    quiet = xs[0].clone()
+    quiet[2] /= 30.0
+    assert rel(ps.decayed_linear_attention(quiet, wf, "r.", m, 1e-5)[300:], want[0][300:]) > 0.05   # the test can tell
+    got = run_in_cuts(MixerHarness(part, rt, hidden, max_positions=1024), xs, CUTS[cut])
+    for a, b in zip(got, want):
+        assert rel(a, b) < tol
+
+
+@pytest.mark.parametrize("cut", list(CUTS))
+@pytest.mark.parametrize("window,page,rot", [(7, 4, 16), (40, 16, 32), (1, 4, 0), (64, 64, 8)])
+@pytest.mark.parametrize("dtype", list(DTYPES))
+def test_capped_window_attention_alone_at_the_window_edges(dtype, window, page, rot, cut):
+    """Values tied to the unrotated keys, rotary on neighbouring pairs of part of the head, capped scores.  One token's
+    input is made large, so that its key's score stands out for half of the heads: the queries just inside the
+    window of it differ grossly from those just outside."""
+    from ferrox_b200.parts.specs import AdjacentRotarySpec, AttentionSpec
+
+    dt, tol = DTYPES[dtype]
+    hidden, H, G, D = 64, 4, 2, 32
+    spec = AttentionSpec(hidden=hidden, n_heads=H, n_kv_heads=G, head_dim=D, qkv_bias=False,
+                         position=AdjacentRotarySpec(rot, 10000.0) if rot else None, window=window, prefix="a.",
+                         softmax_scale=0.2, softcap=6.0, tied_values=True, tensor_names=(("q", "q"), ("k", "k"), ("o", "o")))
+    w = random_tensors(spec, seed=1, std=0.2)
+    assert "a.v" not in w
+    part, rt = load_part(spec, w, dt)
+    g = torch.Generator().manual_seed(7)
+    xs = [torch.randn(n, hidden, generator=g) for n in (150, 70)]
+    p0 = 20
+    xs[0][p0] *= 8.0
+    xs = [x.to(dt).float() for x in xs]
+    m = dict(heads=H, kv_heads=G, dim=D, vdim=D, rot=dict(base=10000.0, dims=rot), scale=0.2, softcap=6.0,
+             mask=dict(size=window))
+    wf = {k: v.float() for k, v in w.items()}
+    want = [ps.capped_window_attention(x, wf, "a.", m, torch.arange(x.shape[0])) for x in xs]
+    if window > 1:
+        inside, outside = want[0][p0 + window - 1], want[0][p0 + window]
+        off_by_one = dict(m, mask=dict(size=window + 1))
+        wrong = ps.capped_window_attention(xs[0], wf, "a.", off_by_one, torch.arange(150))
+        assert rel(wrong[p0 + window], outside) > 0.2       # the test can tell a window that is one token off
+    got = run_in_cuts(MixerHarness(part, rt, hidden, page_size=page, n_pages=40), xs, CUTS[cut])
+    for a, b in zip(got, want):
+        assert rel(a, b) < tol
+
+
+def test_mixer_sum_adds_its_parts_with_their_scales():
+    from ferrox_b200.parts.specs import DecayedLinearAttentionSpec, MixerSumSpec
+
+    hidden = 48
+    a = DecayedLinearAttentionSpec(hidden=hidden, n_heads=2, head_dim=8, value_dim=8, decay=(0.9, 0.5), norm_eps=1e-5, prefix="x.")
+    b = DecayedLinearAttentionSpec(hidden=hidden, n_heads=1, head_dim=16, value_dim=24, decay=(0.99,), norm_eps=1e-5, prefix="y.")
+    spec = MixerSumSpec(mixers=(a, b), scales=(0.6, 1.7))
+    w = random_tensors(spec, seed=3, std=0.3)
+    part, rt = load_part(spec, w, torch.float32)
+    x = torch.randn(19, hidden, generator=torch.Generator().manual_seed(8))
+    wf = {k: v.float() for k, v in w.items()}
+    want = (0.6 * ps.decayed_linear_attention(x, wf, "x.", dict(heads=2, dim=8, vdim=8, decay=[0.9, 0.5]), 1e-5)
+            + 1.7 * ps.decayed_linear_attention(x, wf, "y.", dict(heads=1, dim=16, vdim=24, decay=[0.99]), 1e-5))
+    hs = MixerHarness(part, rt, hidden)
+    assert set(hs.mgr.layer_cache(0).states) == {"0.matrix", "1.matrix"}
+    out = torch.zeros(19, hidden, device=DEV)
+    slot = hs.mgr.open_request()
+    from ferrox_b200.engine.batch import StepEntry, flatten
+    from ferrox_b200.kernels import ops
+    e = StepEntry(slot, [0] * 19)
+    e.start = hs.mgr.reserve_step([slot], [19])[0]
+    batch = flatten([e], torch.device(DEV), hs.status, ops.stream_ptr())
+    part.forward_add(x.to(DEV), out, batch, hs.mgr.layer_cache(0))
+    assert rel(out, want) < 5e-5
+
+
+# ------------------------------------------------------------------ whole models
+def prompts_for(name, n=5, hi=120, seed=0):
+    cfg = CONFIGS[name][0]
+    rng = random.Random(seed)
+    lens = [1, 2, hi] + [rng.randint(3, hi) for _ in range(max(0, n - 3))]
+    return {f"r{i}": [rng.randrange(cfg["vocab"]) for _ in range(L)] for i, L in enumerate(lens)}
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    tmp = tmp_path_factory.mktemp("safepel_models")
+    return {name: make_folder(tmp, name) for name in CONFIGS}
+
+
+@pytest.fixture(scope="module")
+def expected(folders):
+    import plain_qwen2moe as reader
+
+    out = {}
+    for name in CONFIGS:
+        cfg, w = reader.load_model(folders[name], torch.float32)
+        out[name] = (cfg, w, {rid: ps.forward(cfg, w, t) for rid, t in prompts_for(name).items()})
+    return out
+
+
+def engine(folder, dtype, **kw):
+    from ferrox_b200 import Engine
+
+    kw.setdefault("page_size", 8)
+    kw.setdefault("n_pages", 48)
+    kw.setdefault("max_slots", 4)
+    return Engine.from_folder(folder, dtype=dtype, **kw)
+
+
+def compare(got, want, tol, what):
+    for rid in want:
+        assert got[rid].shape == want[rid].shape, (what, rid)
+        assert torch.isfinite(got[rid]).all(), (what, rid)
+        err = float((got[rid] - want[rid]).abs().max() / want[rid].abs().max())
+        assert err < tol, (what, rid, err)
+
+
+RUNS = {
+    "whole": lambda eng, p: ru.run_whole(eng, p),
+    "decoded tail": lambda eng, p: ru.run_tail_decode(eng, p, tail=50),
+    "portions": lambda eng, p: ru.run_portions(eng, p),
+    "decoding together": lambda eng, p: ru.run_decode_together(eng, p, tail=9),
+    "mixed": lambda eng, p: ru.run_mixed(eng, p, seed=3, max_live=3),
+}
+
+
+@pytest.mark.parametrize("run", list(RUNS))
+@pytest.mark.parametrize("name", sorted(CONFIGS))
+@pytest.mark.parametrize("dtype", list(DTYPES))
+def test_model_under_every_cut(folders, expected, dtype, name, run):
+    _, tol = DTYPES[dtype]
+    eng = engine(folders[name], dtype)
+    got = RUNS[run](eng, prompts_for(name))
+    compare(got, expected[name][2], tol, f"{name} {dtype} {run}")
+    eng.cache.check_invariants()
+    assert all(n == eng.cache.groups[k].pool.n_pages for k, n in eng.cache.free_pages().items())   # all given back
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_cuts_agree_with_each_other_to_rounding(folders, name):
+    """32-bit: the recurrences take a request's tokens in the same order whatever the step looks like."""
+    eng = engine(folders[name], "float32")
+    p = prompts_for(name)
+    whole, mixed = ru.run_whole(eng, p), ru.run_mixed(eng, p, seed=5, max_live=4)
+    for rid in p:
+        assert float((whole[rid] - mixed[rid]).abs().max() / whole[rid].abs().max()) < 1e-5
+
+
+@pytest.mark.parametrize("dtype", list(DTYPES))
+def test_long_decoding_past_every_window_with_pages_given_back(folders, dtype):
+    """Three tokens of prompt, then 200 decoded one by one in a pool that holds less than the request: the windowed
+    layers give their old pages back as they go."""
+    import plain_qwen2moe as reader
+
+    _, tol = DTYPES[dtype]
+    cfg, w = reader.load_model(folders["B"], torch.float32)
+    rng = random.Random(9)
+    toks = [rng.randrange(cfg["vocab"]) for _ in range(203)]
+    want = ps.forward(cfg, w, toks)
+    eng = engine(folders["B"], dtype, page_size=8, n_pages=12, max_slots=2)     # 96 positions for 203 tokens
+    c = ru.Collector(eng)
+    c.step({"x": toks[:3]})
+    for t in toks[3:]:
+        c.step({"x": [t]})
+    compare({"x": c.stacked("x")}, {"x": want}, tol, "long decoding")
+    assert max(eng.cache.peak_pages.values()) <= 12
+
+
+@pytest.mark.parametrize("name", sorted(CONFIGS))
+def test_greedy_generation_through_the_scheduler(folders, name):
+    import plain_qwen2moe as reader
+
+    cfg, w = reader.load_model(folders[name], torch.float32)
+    rng = random.Random(4)
+    prompts = [[rng.randrange(cfg["vocab"]) for _ in range(n)] for n in (5, 1, 23)]
+    want = [ps.greedy(cfg, w, p, 12) for p in prompts]
+    eng = engine(folders[name], "float32", n_pages=32)
+    assert eng.graphs is not None            # every part of the model can be captured: decode steps replay graphs
+    got = eng.generate(prompts, max_new_tokens=12, max_batch_tokens=16)     # prompts go in portions
+    assert got == want
+    again = eng.generate(prompts[::-1], max_new_tokens=12)                  # slots and pages used again
+    assert again == want[::-1]
+    bf = engine(folders[name], "bfloat16", n_pages=32).generate(prompts, max_new_tokens=12)
+    assert all(len(g) == 12 for g in bf)
+    # every bfloat16 token is, given the engine's own history, within the bfloat16 tolerance of plain's best
+    for p, g in zip(prompts, bf):
+        logits = ps.forward(cfg, w, (p + g)[:-1])
+        for i, tok in enumerate(g):
+            row = logits[len(p) - 1 + i]
+            assert float(row.max() - row[tok]) <= 2 * 3e-2 * float(logits.abs().max())
+
+
+def test_trace_replay_of_a_safepel_folder(folders, tmp_path):
+    """bin/trace_run picks the model class by config.json and writes the logits that were asked for."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    import numpy as np
+    import plain_qwen2moe as reader
+
+    cfg, w = reader.load_model(folders["A"], torch.float32)
+    toks = [3, 100, 7, 7, 45, 210, 9, 81]
+    want = ps.forward(cfg, w, toks)
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": toks[:5], "want": [0, 4]}], "end": []},
+        {"step": 1, "entries": [{"id": "a", "tokens": toks[5:6], "want": []}], "end": []},
+        {"step": 2, "entries": [{"id": "a", "tokens": toks[6:], "want": [1]}, {"id": "b", "tokens": toks[:2], "want": [1]}],
+         "end": ["a", "b"]},
+    ]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = tmp_path / "out"
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", folders["A"], "--dtype", "float32",
+                        "--out", str(out), "--max-tokens", "128"], input="\n".join(json.dumps(s) for s in steps) + "\n",
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [l for l in r.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2"]
+    assert not (out / "1.f32").exists()
+    s0 = torch.from_numpy(np.fromfile(out / "0.f32", dtype="<f4").reshape(2, -1))
+    s2 = torch.from_numpy(np.fromfile(out / "2.f32", dtype="<f4").reshape(2, -1))
+    assert rel(s0, want[[0, 4]]) < 5e-5 and rel(s2, want[[7, 1]]) < 5e-5
