@@ -46,7 +46,8 @@ int fx_prefill_attention_tc(const void* q, long ldq, int n_tokens, const void* k
                             int n_merges, void* stream);
 int fx_prefill_attention(const void* q, long ldq, const void* k_pages, const void* v_pages, const int* block_table,
                          int table_width, int page_size, const int* tiles, int n_tiles, const int* seq_slot, void* out,
-                         long ldo, int n_heads, int n_kv_heads, int head_dim, int window, float scale, void* stream);
+                         long ldo, int n_heads, int n_kv_heads, int head_dim, int window, float scale, float softcap,
+                         void* stream);
 
 int fx_router_topk(const float* logits, long ld, int n_tokens, int n_experts, int top_k, int renorm, int* ids,
                    float* weights, void* stream);
@@ -90,7 +91,8 @@ int fx_gemm_skinny(const void* X, long ldx, const int* x_rows, const void* W, lo
 int fx_decode_split_mma(const void* q, long ldq, const void* k_pages, const void* v_pages, const int* block_table,
                         int table_width, int page_size, const int* positions, const int* token_seq, const int* seq_slot,
                         float* part_acc, float* part_ml, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
-                        int window, float scale, int split_len, int n_splits, int fresh_positions, void* stream);
+                        int window, float scale, int split_len, int n_splits, int fresh_positions, float softcap,
+                        void* stream);
 int fx_decode_split_tma(const void* q, long ldq, const void* k_pages, const void* v_pages, int n_pages,
                         const int* block_table, int table_width, int page_size, const int* positions,
                         const int* token_seq, const int* seq_slot, float* part_acc, float* part_ml, int n_tokens,
@@ -114,7 +116,10 @@ int fx_decode_attention(const void* q, long ldq, const void* k_pages, const void
                         const int* token_seq, const int* seq_slot, void* out, long ldo, float* part_acc,
                         float* part_ml, int n_tokens, int n_heads, int n_kv_heads, int head_dim, int window,
                         float scale, int split_len, int n_splits, int* status, int* counters, int fresh_positions,
-                        int store_new, int write_pages, const float* cos_sin, void* stream);
+                        int store_new, int write_pages, const float* cos_sin, float softcap, void* stream);
+// softcap c > 0 (fx_paged_attention, fx_prefill_attention, fx_decode_attention): the scaled scores pass through
+// c * tanh(s / c) before the softmax; 0: none.  The kernels that stream pages by TMA take no cap: fx_decode_attention
+// goes to the others, and callers do not give a capped layer to fx_prefill_attention_tc.
 
 // out[i] = mean + stdev * z_i, z the standard normal stream of `key` (random_init.cu; the host restates the rule
 // bit for bit).  dtype: FX_F32 or FX_BF16.

@@ -65,7 +65,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_split_kernel(
     const int* __restrict__ block_table, int table_width, int page_size,
     const int* __restrict__ positions, const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
     float* __restrict__ part_acc, float* __restrict__ part_ml,
-    int n_heads, int n_kv_heads, int head_dim, int window, float scale, int split_len, int n_splits)
+    int n_heads, int n_kv_heads, int head_dim, int window, float scale, int split_len, int n_splits, float cap)
 {
     constexpr int N = Vec<T>::N;
     constexpr int GROUPS = NTHREADS / LPK;
@@ -174,7 +174,9 @@ __global__ void __launch_bounds__(NTHREADS) decode_split_kernel(
                     for (int h = 0; h < GQ; ++h) {
 #pragma unroll
                         for (int o = LPK / 2; o > 0; o >>= 1) sc[u][h] += __shfl_xor_sync(0xffffffffu, sc[u][h], o);
-                        sc[u][h] = valid[u] ? sc[u][h] * scale : -INFINITY;
+                        float sv = sc[u][h] * scale;
+                        if (cap > 0.f) sv = cap * tanhf(sv / cap);   // soft cap on the scaled score
+                        sc[u][h] = valid[u] ? sv : -INFINITY;
                     }
 #pragma unroll
                 for (int h = 0; h < GQ; ++h) {
@@ -281,7 +283,7 @@ __global__ void merge_kernel(const float* __restrict__ part_acc, const float* __
 template <typename T, int LPK, int VPL, int GQ>
 int launch_one(dim3 grid, cudaStream_t s, const T* q, long ldq, const T* k, const T* v, const int* bt, int tw, int ps,
                const int* pos, const int* tseq, const int* sslot, float* pa, float* pm, int nh, int nkv, int d,
-               int window, float scale, int split_len, int n_splits)
+               int window, float scale, int split_len, int n_splits, float softcap)
 {
     auto kern = decode_split_kernel<T, LPK, VPL, GQ>;
     const size_t merge_bytes = sizeof(float) * (NTHREADS / LPK) * GQ * (VPL * LPK * Vec<T>::N);
@@ -294,7 +296,7 @@ int launch_one(dim3 grid, cudaStream_t s, const T* q, long ldq, const T* k, cons
         if (e != cudaSuccess) return (int)e;
     }
     fx_launch_pdl(kern, grid, NTHREADS, smem, s, q, ldq, k, v, bt, tw, ps, pos, tseq, sslot, pa, pm, nh, nkv, d, window, scale,
-                                      split_len, n_splits);
+                                      split_len, n_splits, softcap);
     return fx_launch_status();
 }
 
@@ -314,8 +316,9 @@ int run(const void* q, long ldq, const void* k_pages, const void* v_pages, int n
         int table_width, int page_size, const int* positions, const int* token_seq, const int* seq_slot, void* out,
         long ldo, float* part_acc, float* part_ml, int n_tokens, int n_heads, int n_kv_heads, int head_dim, int window,
         float scale, int split_len, int n_splits, int* status, int* counters, int fresh, int store_new, int write_pages,
-        const float* cos_sin, cudaStream_t s)
+        const float* cos_sin, float softcap, cudaStream_t s)
 {
+    if (softcap > 0.f && store_new) return FX_ERR_SIZE;   // the kernel that stores the step's keys itself takes no cap
     constexpr int N = Vec<T>::N;
     if (head_dim % N || head_dim > MAX_D || head_dim <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads) return FX_ERR_SIZE;
     if (ldq % N || (uintptr_t)q % 16 || (uintptr_t)k_pages % 16 || (uintptr_t)v_pages % 16) return FX_ERR_ALIGN;
@@ -323,7 +326,7 @@ int run(const void* q, long ldq, const void* k_pages, const void* v_pages, int n
         // bfloat16: the tensor-core kernels write the same partial results; the merge below is shared.  The one
         // that streams whole pages by TMA first (head sizes in steps of 64, pages of a multiple of 64 positions).
         int rc_mma = FX_ERR_SIZE;
-        if (n_pages > 0) {
+        if (n_pages > 0 && !(softcap > 0.f)) {   // (the TMA kernel takes no cap on the scores)
             if (n_splits > 32) counters = nullptr;
             rc_mma = fx_decode_split_tma(q, ldq, k_pages, v_pages, n_pages, block_table, table_width, page_size,
                                          positions, token_seq, seq_slot, part_acc, part_ml, n_tokens, n_heads,
@@ -336,7 +339,7 @@ int run(const void* q, long ldq, const void* k_pages, const void* v_pages, int n
         if (rc_mma < 0)
             rc_mma = fx_decode_split_mma(q, ldq, k_pages, v_pages, block_table, table_width, page_size, positions,
                                          token_seq, seq_slot, part_acc, part_ml, n_tokens, n_heads, n_kv_heads,
-                                         head_dim, window, scale, split_len, n_splits, fresh, (void*)s);
+                                         head_dim, window, scale, split_len, n_splits, fresh, softcap, (void*)s);
         if (rc_mma == FX_OK) {
             fx_launch_pdl(merge_kernel<T>, dim3(n_tokens, n_heads), 64, 0, s, part_acc, part_ml, positions, (T*)out, ldo,
                           n_heads, head_dim, n_splits, split_len, window);
@@ -357,7 +360,7 @@ int run(const void* q, long ldq, const void* k_pages, const void* v_pages, int n
 #define FX_GO(LPK, VPL)                                                                                       \
     rc = launch_split<T, LPK, VPL>(gq, grid, s, Q, ldq, K, V, block_table, table_width, page_size, positions, \
                                    token_seq, seq_slot, part_acc, part_ml, n_heads, n_kv_heads, head_dim,    \
-                                   window, scale, split_len, n_splits)
+                                   window, scale, split_len, n_splits, softcap)
     if (vecs <= 4) { FX_GO(4, 1); }
     else if (vecs <= 8) { FX_GO(8, 1); }
     else if (vecs <= 16) { FX_GO(16, 1); }
@@ -379,7 +382,7 @@ extern "C" int fx_decode_attention(const void* q, long ldq, const void* k_pages,
                                    float* part_acc, float* part_ml, int n_tokens, int n_heads, int n_kv_heads,
                                    int head_dim, int window, float scale, int split_len, int n_splits, int* status,
                                    int* counters, int fresh_positions, int store_new, int write_pages,
-                                   const float* cos_sin, void* stream)
+                                   const float* cos_sin, float softcap, void* stream)
 {
     if (n_tokens <= 0) return FX_OK;
     if (split_len < 0 || n_splits <= 0) return FX_ERR_SIZE;
@@ -387,11 +390,11 @@ extern "C" int fx_decode_attention(const void* q, long ldq, const void* k_pages,
     if (dtype == FX_F32)
         return run<float>(q, ldq, k_pages, v_pages, n_pages, block_table, table_width, page_size, positions, token_seq,
                           seq_slot, out, ldo, part_acc, part_ml, n_tokens, n_heads, n_kv_heads, head_dim, window, scale,
-                          split_len, n_splits, status, counters, fresh_positions, store_new, write_pages, cos_sin, s);
+                          split_len, n_splits, status, counters, fresh_positions, store_new, write_pages, cos_sin, softcap, s);
     if (dtype == FX_BF16)
         return run<bf16>(q, ldq, k_pages, v_pages, n_pages, block_table, table_width, page_size, positions, token_seq,
                          seq_slot, out, ldo, part_acc, part_ml, n_tokens, n_heads, n_kv_heads, head_dim, window, scale,
-                         split_len, n_splits, status, counters, fresh_positions, store_new, write_pages, cos_sin, s);
+                         split_len, n_splits, status, counters, fresh_positions, store_new, write_pages, cos_sin, softcap, s);
     return FX_ERR_DTYPE;
 }
 
@@ -446,10 +449,10 @@ extern "C" int fx_decode_attention_noalloc(const void* q, long ldq, const void* 
     if (dtype == FX_F32)
         return run<float>(q, ldq, k_pages, v_pages, 0, block_table, table_width, page_size, positions, token_seq, seq_slot,
                           out, ldo, part_acc, part_ml, n_tokens, n_heads, n_kv_heads, head_dim, window, scale,
-                          split_len, n_splits, nullptr, nullptr, 0, 0, 0, nullptr, s);
+                          split_len, n_splits, nullptr, nullptr, 0, 0, 0, nullptr, 0.f, s);
     if (dtype == FX_BF16)
         return run<bf16>(q, ldq, k_pages, v_pages, 0, block_table, table_width, page_size, positions, token_seq, seq_slot,
                          out, ldo, part_acc, part_ml, n_tokens, n_heads, n_kv_heads, head_dim, window, scale,
-                         split_len, n_splits, nullptr, nullptr, 0, 0, 0, nullptr, s);
+                         split_len, n_splits, nullptr, nullptr, 0, 0, 0, nullptr, 0.f, s);
     return FX_ERR_DTYPE;
 }

@@ -58,7 +58,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_mma_kernel(
     const int* __restrict__ positions, const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
     float* __restrict__ part_acc, float* __restrict__ part_ml,
     int n_heads, int n_kv_heads, int head_dim, int window, float scale_log2e, float scale, int split_len, int n_splits,
-    int fresh)
+    int fresh, float cap, float cap_mul)
 {
     // fresh <= 0: nothing is known about the kernel before this one, so nothing is read before it has finished.
     if (fresh <= 0) fx_pdl_wait();
@@ -183,6 +183,12 @@ __global__ void __launch_bounds__(NTHREADS) decode_mma_kernel(
                     mma16816(s[1], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b2, b3);
                 }
             }
+            if (cap > 0.f) {   // soft cap: cap * tanh(scaled score / cap); the scale is inside cap_mul
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) s[j][e] = cap * tanhf(s[j][e] * cap_mul);
+            }
             // keys past the range or without a page do not count
             float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
@@ -270,15 +276,18 @@ __global__ void __launch_bounds__(NTHREADS) decode_mma_kernel(
 template <int DMAX>
 int launch(dim3 grid, size_t smem, cudaStream_t s, const bf16* q, long ldq, const bf16* k, const bf16* v, const int* bt,
            int tw, int ps, const int* pos, const int* tseq, const int* sslot, float* pa, float* pm, int nh, int nkv, int d,
-           int window, float scale, int split_len, int n_splits, int fresh)
+           int window, float scale, int split_len, int n_splits, int fresh, float softcap)
 {
+    // capped scores: the kernel turns the raw products into cap * tanh(scale * s / cap); what follows sees scale 1
+    const float cap = softcap > 0.f ? softcap : 0.f, cap_mul = softcap > 0.f ? scale / softcap : 0.f;
+    if (softcap > 0.f) scale = 1.0f;
     auto kern = decode_mma_kernel<DMAX>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
     fx_launch_pdl(kern, grid, NTHREADS, smem, s, q, ldq, k, v, bt, tw, ps, pos, tseq, sslot, pa, pm, nh, nkv, d, window,
-                  scale * 1.4426950408889634f, scale, split_len, n_splits, fresh);
+                  scale * 1.4426950408889634f, scale, split_len, n_splits, fresh, cap, cap_mul);
     return fx_launch_status();
 }
 
@@ -290,7 +299,7 @@ extern "C" int fx_decode_split_mma(const void* q, long ldq, const void* k_pages,
                                    const int* block_table, int table_width, int page_size, const int* positions,
                                    const int* token_seq, const int* seq_slot, float* part_acc, float* part_ml,
                                    int n_tokens, int n_heads, int n_kv_heads, int head_dim, int window, float scale,
-                                   int split_len, int n_splits, int fresh_positions, void* stream)
+                                   int split_len, int n_splits, int fresh_positions, float softcap, void* stream)
 {
     if (n_tokens <= 0) return FX_OK;
     if (head_dim % 16 || head_dim <= 0 || head_dim > 256 || n_kv_heads <= 0 || n_heads % n_kv_heads) return FX_ERR_SIZE;
@@ -307,10 +316,10 @@ extern "C" int fx_decode_split_mma(const void* q, long ldq, const void* k_pages,
     const bf16* Q = (const bf16*)q; const bf16* K = (const bf16*)k_pages; const bf16* V = (const bf16*)v_pages;
     if (head_dim <= 64)
         return launch<64>(grid, smem, s, Q, ldq, K, V, block_table, table_width, page_size, positions, token_seq, seq_slot,
-                          part_acc, part_ml, n_heads, n_kv_heads, head_dim, window, scale, split_len, n_splits, fresh_positions);
+                          part_acc, part_ml, n_heads, n_kv_heads, head_dim, window, scale, split_len, n_splits, fresh_positions, softcap);
     if (head_dim <= 128)
         return launch<128>(grid, smem, s, Q, ldq, K, V, block_table, table_width, page_size, positions, token_seq, seq_slot,
-                           part_acc, part_ml, n_heads, n_kv_heads, head_dim, window, scale, split_len, n_splits, fresh_positions);
+                           part_acc, part_ml, n_heads, n_kv_heads, head_dim, window, scale, split_len, n_splits, fresh_positions, softcap);
     return launch<256>(grid, smem, s, Q, ldq, K, V, block_table, table_width, page_size, positions, token_seq, seq_slot,
-                       part_acc, part_ml, n_heads, n_kv_heads, head_dim, window, scale, split_len, n_splits, fresh_positions);
+                       part_acc, part_ml, n_heads, n_kv_heads, head_dim, window, scale, split_len, n_splits, fresh_positions, softcap);
 }

@@ -56,7 +56,7 @@ __global__ void __launch_bounds__(NTHREADS) prefill_attention_kernel(
     const bf16* __restrict__ q, long ldq, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
     const int* __restrict__ block_table, int table_width, int page_size, const int* __restrict__ tiles,
     const int* __restrict__ seq_slot, bf16* __restrict__ out, long ldo, int n_heads, int n_kv_heads, int head_dim,
-    int window, float scale_log2e)
+    int window, float scale_log2e, float cap, float cap_mul)
 {
     extern __shared__ __align__(16) uint8_t smem[];
     const int pitch = head_dim * 2 + 16;                 // bytes per row: 16 bytes of padding spread the banks
@@ -174,6 +174,12 @@ __global__ void __launch_bounds__(NTHREADS) prefill_attention_kernel(
                     }
                 }
             }
+            if (cap > 0.f) {   // soft cap: cap * tanh(scaled score / cap); the scale is inside cap_mul
+#pragma unroll
+                for (int j = 0; j < BKEY / 8; ++j)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) s[j][e] = cap * tanhf(s[j][e] * cap_mul);
+            }
             // ---- mask by absolute position, online softmax ---------------------------
             const int lo0 = window > 0 ? p_row0 - window + 1 : 0, lo1 = window > 0 ? p_row1 - window + 1 : 0;
             float mx0 = -INFINITY, mx1 = -INFINITY;
@@ -251,14 +257,14 @@ __global__ void __launch_bounds__(NTHREADS) prefill_attention_kernel(
 template <int DMAX>
 int launch(dim3 grid, size_t smem, cudaStream_t s, const bf16* q, long ldq, const bf16* k, const bf16* v, const int* bt,
            int tw, int ps, const int* tiles, const int* seq_slot, bf16* out, long ldo, int nh, int nkv, int d, int window,
-           float scale_log2e)
+           float scale_log2e, float cap, float cap_mul)
 {
     auto kern = prefill_attention_kernel<DMAX>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    kern<<<grid, NTHREADS, smem, s>>>(q, ldq, k, v, bt, tw, ps, tiles, seq_slot, out, ldo, nh, nkv, d, window, scale_log2e);
+    kern<<<grid, NTHREADS, smem, s>>>(q, ldq, k, v, bt, tw, ps, tiles, seq_slot, out, ldo, nh, nkv, d, window, scale_log2e, cap, cap_mul);
     return fx_launch_status();
 }
 
@@ -268,7 +274,7 @@ int launch(dim3 grid, size_t smem, cudaStream_t s, const bf16* q, long ldq, cons
 extern "C" int fx_prefill_attention(const void* q, long ldq, const void* k_pages, const void* v_pages,
                                     const int* block_table, int table_width, int page_size, const int* tiles,
                                     int n_tiles, const int* seq_slot, void* out, long ldo, int n_heads, int n_kv_heads,
-                                    int head_dim, int window, float scale, void* stream)
+                                    int head_dim, int window, float scale, float softcap, void* stream)
 {
     if (n_tiles <= 0) return FX_OK;
     if (head_dim % 16 || head_dim <= 0 || head_dim > 256 || n_kv_heads <= 0 || n_heads % n_kv_heads) return FX_ERR_SIZE;
@@ -278,14 +284,16 @@ extern "C" int fx_prefill_attention(const void* q, long ldq, const void* k_pages
     const size_t smem = (size_t)(BQ + 4 * BKEY) * (head_dim * 2 + 16);
     dim3 grid(n_tiles, n_heads);
     cudaStream_t s = (cudaStream_t)stream;
-    const float sl = scale * 1.4426950408889634f;
+    // capped scores: the kernel turns the raw products into cap * tanh(scale * s / cap); what follows sees scale 1
+    const float cap = softcap > 0.f ? softcap : 0.f, cap_mul = softcap > 0.f ? scale / softcap : 0.f;
+    const float sl = (softcap > 0.f ? 1.0f : scale) * 1.4426950408889634f;
     const bf16* Q = (const bf16*)q; const bf16* K = (const bf16*)k_pages; const bf16* V = (const bf16*)v_pages;
     if (head_dim <= 64)
         return launch<64>(grid, smem, s, Q, ldq, K, V, block_table, table_width, page_size, tiles, seq_slot, (bf16*)out,
-                          ldo, n_heads, n_kv_heads, head_dim, window, sl);
+                          ldo, n_heads, n_kv_heads, head_dim, window, sl, cap, cap_mul);
     if (head_dim <= 128)
         return launch<128>(grid, smem, s, Q, ldq, K, V, block_table, table_width, page_size, tiles, seq_slot, (bf16*)out,
-                           ldo, n_heads, n_kv_heads, head_dim, window, sl);
+                           ldo, n_heads, n_kv_heads, head_dim, window, sl, cap, cap_mul);
     return launch<256>(grid, smem, s, Q, ldq, K, V, block_table, table_width, page_size, tiles, seq_slot, (bf16*)out, ldo,
-                       n_heads, n_kv_heads, head_dim, window, sl);
+                       n_heads, n_kv_heads, head_dim, window, sl, cap, cap_mul);
 }

@@ -59,7 +59,7 @@ _SIGNATURES = {
     "fx_conv_tail_update": [_P, _I, _L, _I, _I, _P, _P, _P, _I, _I, _P],
     "fx_state_scan": [_P, _L, _P, _L, _P, _L, _I, _I, _P, _L, _P, _P, _P, _L, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "fx_gated_group_norm": [_P, _P, _I, _L, _P, _I, _F, _I, _P, _I, _I, _I, _I, _P],
-    "fx_prefill_attention": [_P, _L, _P, _P, _P, _I, _I, _P, _I, _P, _P, _L, _I, _I, _I, _I, _F, _P],
+    "fx_prefill_attention": [_P, _L, _P, _P, _P, _I, _I, _P, _I, _P, _P, _L, _I, _I, _I, _I, _F, _F, _P],
     "fx_prefill_attention_tc": [_P, _L, _I, _P, _P, _I, _P, _I, _I, _P, _I, _P, _P, _L, _I, _I, _I, _I, _F, _P, _P, _P,
                                 _P, _I, _P],
     "fx_router_topk": [_P, _L, _I, _I, _I, _I, _P, _P, _P],
@@ -68,7 +68,7 @@ _SIGNATURES = {
     "fx_gemm_slab": [_P, _L, _P, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _P, _P],
     "fx_gemm_skinny": [_P, _L, _P, _P, _L, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _P, _I, _I, _I, _P],
     "fx_decode_attention": [_P, _L, _P, _P, _I, _I, _P, _I, _I, _P, _P, _P, _P, _L, _P, _P, _I, _I, _I, _I, _I, _F, _I,
-                            _I, _P, _P, _I, _I, _I, _P, _P],
+                            _I, _P, _P, _I, _I, _I, _P, _F, _P],
     "fx_argmax": [_P, _L, _I, _I, _P, _P],
     "fx_repetition_penalty": [_P, _L, _I, _I, _P, _P, _P, _P],
     "fx_sample": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P],
@@ -471,24 +471,19 @@ def paged_attention(q, k_pages, v_pages, block_table, page_size, positions, toke
     return out
 
 
-def softcap_ok(qkv, few_new_tokens: bool, head_dim: int, page_size: int) -> bool:
-    """Whether the kernel that would run these operands (split keys for few new tokens a request, tiles of queries
-    otherwise) takes a cap on the scores; if not, :func:`paged_attention` does."""
-    return False
-
-
 PREFILL_TILE = 64
 
 
 def prefill_attention(q, k_pages, v_pages, block_table, page_size, tiles, seq_slot, out, n_heads, n_kv_heads, head_dim,
-                      window, scale, stream=None):
+                      window, scale, stream=None, softcap=None):
     """Flash attention of prompt portions (bfloat16).  ``tiles``: int32 [n, 4] rows of
     (first flat token, rows <= 64, entry index, absolute position of the first row)."""
     if q.dtype != torch.bfloat16:
         raise KernelError("prefill_attention is a bfloat16 kernel")
     call("fx_prefill_attention", _ptr(q), _rows(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
          block_table.shape[1], page_size, _ptr(tiles), tiles.shape[0], _ptr(seq_slot), _ptr(out), _rows(out), n_heads,
-         n_kv_heads, head_dim, int(window or 0), float(scale), stream if stream is not None else stream_ptr())
+         n_kv_heads, head_dim, int(window or 0), float(scale), float(softcap or 0.0),
+         stream if stream is not None else stream_ptr())
     return out
 
 
@@ -734,8 +729,10 @@ def decode_store_ok(qkv, k_pages, head_dim: int, page_size: int) -> bool:
 
 def decode_attention(q, k_pages, v_pages, block_table, page_size, positions, token_seq, seq_slot, out, n_heads,
                      n_kv_heads, head_dim, window, scale, split_len, n_splits, part_acc, part_ml, status=None,
-                     counters=None, stream=None, fresh_positions=0, store_new=False, write_pages=True, cos_sin=None):
-    """``counters``: zeroed int32 scratch that the call leaves zeroed, at least tokens x ceil(group / 16) x kv heads;
+                     counters=None, stream=None, fresh_positions=0, store_new=False, write_pages=True, cos_sin=None,
+                     softcap=None):
+    """``softcap`` c: the scaled scores pass through c * tanh(s / c) (the kernel that streams pages by TMA does not
+    take one: the call goes to the others).  ``counters``: zeroed int32 scratch that the call leaves zeroed, at least tokens x ceil(group / 16) x kv heads;
     with it the kernel that streams pages by TMA merges the key ranges itself (one kernel instead of two).
     ``fresh_positions``: 0 assumes nothing about the kernel launched just before on the stream.  N > 0 promises that
     that kernel wrote, of all this call reads, only the queries and the keys and values of at most the last N
@@ -746,7 +743,7 @@ def decode_attention(q, k_pages, v_pages, block_table, page_size, positions, tok
     value put where the attention reads them and, if ``write_pages``, into the pages."""
     global _launches
     T = q.shape[0]
-    per_sm = decode_tma_blocks_per_sm(q.dtype, head_dim, page_size)
+    per_sm = 0 if softcap else decode_tma_blocks_per_sm(q.dtype, head_dim, page_size)
     blocks = T * n_kv_heads * -(-(n_heads // n_kv_heads) // 16)
     # Merging in the kernel pays while all blocks run at the same time: the count and the fence lengthen the end of
     # every block, which costs nothing only where no other block waits for its place.
@@ -759,8 +756,14 @@ def decode_attention(q, k_pages, v_pages, block_table, page_size, positions, tok
          _ptr(block_table), block_table.shape[1], page_size, _ptr(positions), _ptr(token_seq), _ptr(seq_slot),
          _ptr(out), _rows(out), _ptr(part_acc), _ptr(part_ml), T, n_heads, n_kv_heads, head_dim, int(window or 0),
          float(scale), split_len, n_splits, _ptr(status), _ptr(counters), int(fresh_positions), int(store_new),
-         int(write_pages), _ptr(cos_sin), stream if stream is not None else stream_ptr())
+         int(write_pages), _ptr(cos_sin), float(softcap or 0.0), stream if stream is not None else stream_ptr())
     return out
+
+
+def decode_ok(q, head_dim: int) -> bool:
+    """Whether the split-key kernels take these operands (heads of whole 16-byte vectors, aligned rows)."""
+    n = 8 if q.dtype == torch.bfloat16 else 4
+    return head_dim % n == 0 and q.stride(0) % n == 0 and q.data_ptr() % 16 == 0
 
 
 TC_MAX_GROUPS = 1024        # experts the grouped tcgen05 kernel keeps its tile table for (gemm_tc.cu)

@@ -147,24 +147,18 @@ class GqaAttention(Mixer):
         # A decode step of one token a request: where the attention kernel can, it rotates the queries and rotates and
         # stores the keys and values itself (one launch less on every layer's path); else the position part does.
         in_kernel = None
-        if (batch.max_new == 1 and T <= ROTARY_IN_DECODE_KERNEL_MAX_TOKENS
+        capped = self.softcap is not None
+        if (batch.max_new == 1 and T <= ROTARY_IN_DECODE_KERNEL_MAX_TOKENS and not capped
                 and ops.decode_store_ok(qkv, cache.k, s.head_dim, cache.page_size)):
             in_kernel = self.position.in_decode_kernel(batch, s.head_dim)
         if in_kernel is None:
             self.position.rotate_and_store(qkv, batch, cache, s.n_heads, s.n_kv_heads, s.head_dim)
         attn = self.rt.empty(T, self.q_size)
-        if self.softcap is not None and not ops.softcap_ok(qkv, batch.max_new <= DECODE_ATTENTION_MAX_NEW, s.head_dim,
-                                                           cache.page_size):
-            # capped scores, where the faster kernels do not take them: a warp per (token, head)
-            ops.paged_attention(
-                qkv, cache.k, cache.v, cache.block_table, cache.page_size, batch.positions, batch.token_seq,
-                batch.seq_slot, attn, s.n_heads, s.n_kv_heads, s.head_dim, s.window, self.scale, stream=batch.stream,
-                softcap=self.softcap,
-            )
-        elif batch.max_new <= DECODE_ATTENTION_MAX_NEW:
+        if batch.max_new <= DECODE_ATTENTION_MAX_NEW and ops.decode_ok(qkv, s.head_dim):
             # few query tokens: split each request's keys over many blocks
             group = s.n_heads // s.n_kv_heads
-            per_sm = ops.decode_tma_blocks_per_sm(qkv.dtype, s.head_dim, cache.page_size)
+            # (capped scores: not the kernel that streams pages by TMA)
+            per_sm = 0 if capped else ops.decode_tma_blocks_per_sm(qkv.dtype, s.head_dim, cache.page_size)
             # blocks per token: the tensor-core kernels take 16 query heads of a kv head at a time, the CUDA-core one 8
             kv_blocks = s.n_kv_heads * -(-group // (16 if qkv.dtype == torch.bfloat16 else 8))
             # the most keys a token reads: the context limit, or a window (with the 64-key blocks it straddles)
@@ -184,8 +178,9 @@ class GqaAttention(Mixer):
                 # k, v of the step's own positions, max_new of a request
                 fresh_positions=batch.max_new,
                 store_new=in_kernel is not None, write_pages=cache.writes, cos_sin=in_kernel[0] if in_kernel else None,
+                softcap=self.softcap,
             )
-        elif ops.prefill_tc_ok(qkv, attn, cache.k, cache.page_size, s.head_dim):
+        elif not capped and ops.prefill_tc_ok(qkv, attn, cache.k, cache.page_size, s.head_dim):
             # prompt portions: tiles of 256 queries (long ones cut into runs of key blocks), tcgen05
             items, merges, parts = prefill_tc_plan(batch, s.window, s.n_heads)
             part_o = part_ml = None
@@ -202,13 +197,14 @@ class GqaAttention(Mixer):
             ops.prefill_attention(
                 qkv, cache.k, cache.v, cache.block_table, cache.page_size, query_tiles(batch, ops.PREFILL_TILE),
                 batch.seq_slot, attn,
-                s.n_heads, s.n_kv_heads, s.head_dim, s.window, self.scale, stream=batch.stream,
+                s.n_heads, s.n_kv_heads, s.head_dim, s.window, self.scale, stream=batch.stream, softcap=self.softcap,
             )
         else:
             # 32-bit, and head sizes that are no multiple of 16: a warp per (token, head)
             ops.paged_attention(
                 qkv, cache.k, cache.v, cache.block_table, cache.page_size, batch.positions, batch.token_seq,
                 batch.seq_slot, attn, s.n_heads, s.n_kv_heads, s.head_dim, s.window, self.scale, stream=batch.stream,
+                softcap=self.softcap,
             )
         # (the attention's last blocks only add up key ranges: the memory system is idle under them)
         ops.linear(attn, self.w_o, h, accumulate=accumulate, status=batch.status, stream=batch.stream,
