@@ -2,6 +2,7 @@
 """Decode and prefill throughput of the engine on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--shape a2.7b|a14b] [--repeats 3]
+    python bench.py --designs        (the Safepel design beside the dense decoder at equal sizes; its own JSON line)
 
 Default workload: the layer sizes of the Qwen1.5-MoE-A2.7B shape (24 layers, hidden
 2048, 16 heads of 128, 60 experts top-4 of width 1408, shared expert 5632, vocab
@@ -156,6 +157,140 @@ def prefill_flops(cfg, T, n_layers):
     return n_layers * (per_tok * T + attn) + 2 * H * cfg.vocab_size  # head at the last position
 
 
+# ---- --designs: the Safepel design beside the dense Qwen2 decoder at equal size ---------------------------------
+def safepel_shape(width, layers, ff, vocab=32768, window=1024):
+    """Layer sizes that resemble a real model's: heads of 128, delta and parallel layers in turn."""
+    h = width // 128
+    delta = {"type": "delta", "mixer": {"heads": h, "kv_heads": max(1, h // 2), "dim": 128, "vdim": 128, "conv": 4},
+             "mlp": {"kind": "dense", "ff": ff}}
+    par = {"type": "parallel", "mlp": {"kind": "dense", "ff": ff}, "mixer": {
+        "left": {"heads": h, "kv_heads": max(1, h // 4), "dim": 128, "vdim": 128, "mask": {"size": window},
+                 "rot": {"dims": 64, "base": 500000.0}, "scale": 128 ** -0.5, "softcap": 30.0},
+        "right": {"heads": h, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** -(3 + 8 * i / max(1, h - 1)) for i in range(h)]},
+        "left_scale": 1.0, "right_scale": 1.0}}
+    return {"architecture": "Safepel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "logit_scale": 1.0,
+            "max_positions": CONTEXT, "layers": [delta if i % 2 == 0 else par for i in range(layers)]}
+
+
+def dense_like(width, layers, ff, vocab=32768):
+    """The closest existing model, a Qwen2 decoder without experts, with as many parameters: the mixers of the
+    Safepel shape hold 11,520 x width parameters a layer on average against 5,120 x width here; the difference
+    goes into the feed-forward."""
+    h = width // 128
+    inter = (ff + (11520 - 5120) * width // 2048 // 3 + 63) // 64 * 64
+    return dict(architectures=["Qwen2MoeForCausalLM"], num_hidden_layers=layers, hidden_size=width,
+                num_attention_heads=h, num_key_value_heads=max(1, h // 4), head_dim=128, num_experts=0,
+                intermediate_size=inter, qkv_bias=True, vocab_size=vocab, rope_theta=1000000.0, rms_norm_eps=1e-6,
+                tie_word_embeddings=False, max_position_embeddings=CONTEXT)
+
+
+def compare_designs(args) -> int:
+    """Prefill and decode throughput of the Safepel design and of the dense decoder at a few equal sizes (random
+    bfloat16 weights), with the device time of every class of kernel from a traced pass beside them."""
+    import torch
+
+    from ferrox_b200 import Engine, StepEntry
+    from ferrox_b200.kernels import ops
+
+    gen = torch.Generator().manual_seed(1)
+    ps, batch, steps = args.page_size, args.batch, max(8, min(args.steps, 64))
+    sizes = [(1024, 8, 2816), (2048, 8, 5632), (4096, 4, 11264)]
+    if args.layers:
+        sizes = [(w, args.layers, ff) for w, _, ff in sizes]
+
+    def timed(fn):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b)
+
+    def measure(cfg):
+        n_pages = (PREFILL_TOKENS + steps + 80) // ps * (batch + 1) + 8
+        kw = dict(seed=0, dtype="bfloat16", on_device=True, page_size=ps, n_pages=n_pages, max_slots=batch + 1,
+                  max_positions=CONTEXT)
+        eng = Engine.from_random(cfg, **kw)
+        V = eng.spec.vocab_size
+        prompt = lambda n: torch.randint(0, V, (n,), generator=gen).tolist()
+        out = {"weight_bytes": eng.model.weight_bytes()}
+
+        def prefill_once():
+            slot = eng.open_request()
+            eng.step([StepEntry(slot, prompt(PREFILL_TOKENS), want=[PREFILL_TOKENS - 1])], check=False)
+            eng.close_request(slot)
+
+        for _ in range(3):
+            prefill_once()
+        runs = [timed(prefill_once) for _ in range(3)]
+        out["prefill"] = {"tokens": PREFILL_TOKENS, "ms": statistics.median(runs), "runs_ms": runs,
+                          "tokens_per_s": PREFILL_TOKENS / (statistics.median(runs) / 1e3)}
+        for b in sorted({1, batch}):
+            slots = []
+            for _ in range(b):
+                slot = eng.open_request()
+                eng.step([StepEntry(slot, prompt(PREFILL_TOKENS), want=[])], check=False)
+                slots.append(slot)
+            ids = [1] * b
+            dev = torch.empty(b, dtype=torch.int32, device="cuda")
+
+            def one_step():
+                nonlocal ids
+                logits = eng.step([StepEntry(s, [t], want=[0]) for s, t in zip(slots, ids)], check=False)
+                ids = ops.argmax(logits, dev).tolist()
+
+            for _ in range(max(3, args.warmup)):
+                one_step()
+            regions = [timed(lambda: [one_step() for _ in range(steps)]) / steps for _ in range(3)]
+            ms = statistics.median(regions)
+            # what a step must read: every weight once and the requests' states and windows of keys
+            state = sum(t.numel() * t.element_size() // t.shape[0] for named in eng.cache._named_state
+                        for t in (named or {}).values())
+            out[f"decode_b{b}"] = {"ms_per_step": ms, "tokens_per_s": b / (ms / 1e3), "regions_ms": regions,
+                                   "graph": eng.graphs is not None and b in eng.graphs.graphs,
+                                   "weights_gbs": out["weight_bytes"] / (ms / 1e3) / 1e9,
+                                   "state_bytes_per_request": state}
+            for s in slots:
+                eng.close_request(s)
+        del eng
+        # a traced pass (launches timed one by one, no graphs) for the share of every class of kernel
+        Engine.trace_start()
+        try:
+            eng = Engine.from_random(cfg, **kw)
+            slot = eng.open_request()
+            toks = prompt(PREFILL_TOKENS)
+            eng.step([StepEntry(slot, toks, want=[PREFILL_TOKENS - 1])], check=False)
+            eng.close_request(slot)
+            Engine.trace_stop()
+            Engine.trace_start()
+            slot = eng.open_request()
+            eng.step([StepEntry(slot, toks, want=[PREFILL_TOKENS - 1])], check=False)
+            pre = Engine.trace_stop()
+            Engine.trace_start()
+            for _ in range(4):
+                eng.step([StepEntry(slot, [1], want=[0])], check=False)
+            dec = Engine.trace_stop()
+        finally:
+            if ops.trace_enabled():
+                Engine.trace_stop()
+        out["prefill_kernels_ms"] = {k: round(v[1], 4) for k, v in sorted(pre.items(), key=lambda kv: -kv[1][1])}
+        out["decode_b1_kernels_us"] = {k: round(v[1] / 4 * 1e3, 2) for k, v in sorted(dec.items(), key=lambda kv: -kv[1][1])}
+        del eng
+        return out
+
+    pk = peaks()
+    rows = []
+    for width, layers, ff in sizes:
+        a, b = safepel_shape(width, layers, ff), dense_like(width, layers, ff)
+        rows.append({"width": width, "layers": layers, "ff": ff, "dense_ff": b["intermediate_size"],
+                     "safepel": measure(a), "dense": measure(b)})
+    print(json.dumps({"designs": "Safepel beside the dense Qwen2 decoder at equal size", "dtype": "bf16", "batch": batch,
+                      "prompt_tokens": PREFILL_TOKENS, "decode_steps_timed": steps, "peaks": pk,
+                      "data": "synthetic: random N(0,0.02) weights, uniform random token ids", "sizes": rows}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -169,12 +304,17 @@ def main() -> int:
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--page-size", type=int, default=64)
     ap.add_argument("--repeats", type=int, default=3, help="timed regions of --steps steps each; the median counts")
+    ap.add_argument("--designs", action="store_true",
+                    help="instead of the default workload: prefill and decode of the Safepel design beside the dense "
+                         "Qwen2 decoder at a few equal sizes, with device time per class of kernel")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not built")
         return 2
+    if args.designs:
+        return compare_designs(args)
     if args.warmup < 3:
         args.warmup = 3
 

@@ -195,19 +195,21 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanArgs
         for (int tt = 0; tt < nt; ++tt) {
             const float gt = g_s[tt];
             float u = v_s[tt][cl];
+            // (four partial sums a dot product: the chain of dependent additions is a quarter as long)
             if (DELTA) {
-                float dot = 0.f;
+                float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
 #pragma unroll
                 for (int i = 0; i < RPL; i += 4) {
                     const float4 kk = *reinterpret_cast<const float4*>(&k_s[tt][(i >> 2) * 4 * R + part * 4]);
                     S[i] *= gt; S[i + 1] *= gt; S[i + 2] *= gt; S[i + 3] *= gt;
-                    dot = fmaf(S[i], kk.x, dot); dot = fmaf(S[i + 1], kk.y, dot);
-                    dot = fmaf(S[i + 2], kk.z, dot); dot = fmaf(S[i + 3], kk.w, dot);
+                    d0 = fmaf(S[i], kk.x, d0); d1 = fmaf(S[i + 1], kk.y, d1);
+                    d2 = fmaf(S[i + 2], kk.z, d2); d3 = fmaf(S[i + 3], kk.w, d3);
                 }
+                float dot = (d0 + d1) + (d2 + d3);
                 for (int o = R >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
                 u = b_s[tt] * (u - dot);
             }
-            float rd = 0.f;
+            float r0s = 0.f, r1s = 0.f, r2s = 0.f, r3s = 0.f;
 #pragma unroll
             for (int i = 0; i < RPL; i += 4) {
                 const int at = (i >> 2) * 4 * R + part * 4;
@@ -220,9 +222,10 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanArgs
                     S[i] = fmaf(gt, S[i], kk.x * u); S[i + 1] = fmaf(gt, S[i + 1], kk.y * u);
                     S[i + 2] = fmaf(gt, S[i + 2], kk.z * u); S[i + 3] = fmaf(gt, S[i + 3], kk.w * u);
                 }
-                rd = fmaf(S[i], qq.x, rd); rd = fmaf(S[i + 1], qq.y, rd);
-                rd = fmaf(S[i + 2], qq.z, rd); rd = fmaf(S[i + 3], qq.w, rd);
+                r0s = fmaf(S[i], qq.x, r0s); r1s = fmaf(S[i + 1], qq.y, r1s);
+                r2s = fmaf(S[i + 2], qq.z, r2s); r3s = fmaf(S[i + 3], qq.w, r3s);
             }
+            float rd = (r0s + r1s) + (r2s + r3s);
             for (int o = R >> 1; o > 0; o >>= 1) rd += __shfl_xor_sync(0xffffffffu, rd, o);
             if (live && part == 0) a.out[(long)(c0 + tt) * a.ldo + (long)h * V + col] = rd;
         }
