@@ -59,6 +59,14 @@ def _unescape(s: str) -> str:
     return s.replace("\\n", "\n").replace("\\t", "\t").replace("\\r", "\r").replace("\\\\", "\\")
 
 
+def _default_tokens(config: dict) -> int:
+    """Positions the cache pool is made for when neither -c nor a page count is given: the model's own position
+    limit as its architecture states it, at most 32,768 (designs without a limit of their own state a large one)."""
+    from .config.registry import resolve
+
+    return min(resolve(config)[1].max_positions, 32768)
+
+
 def main(argv=None) -> int:
     argv = list(sys.argv[1:] if argv is None else argv)
     if argv and argv[0] == "run":
@@ -84,7 +92,7 @@ def main(argv=None) -> int:
         if args.num_pages:
             cache["n_pages"] = args.num_pages
         else:
-            cache["max_tokens"] = args.ctx_size or cfg["max_position_embeddings"]
+            cache["max_tokens"] = args.ctx_size or _default_tokens(cfg)
         eng = Engine.from_random(cfg, seed=args.weights_seed, dtype=args.dtype, **cache)
     else:
         from .config.schema import load_json
@@ -92,7 +100,7 @@ def main(argv=None) -> int:
         if args.num_pages:
             cache["n_pages"] = args.num_pages
         else:
-            cache["max_tokens"] = args.ctx_size or load_json(args.model)["max_position_embeddings"]
+            cache["max_tokens"] = args.ctx_size or _default_tokens(load_json(args.model))
         eng = Engine.from_folder(args.model, dtype=args.dtype, **cache)
     print(f"ferrox: loaded in {time.time() - t0:.2f}s", file=sys.stderr)
 

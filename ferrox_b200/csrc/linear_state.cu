@@ -154,6 +154,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanArgs
     __shared__ __align__(16) float q_s[CH][MAX_DP];
     __shared__ float v_s[CH][SCAN_THREADS];
     __shared__ float g_s[CH], b_s[CH];
+    __shared__ float rd_s[CH][SCAN_THREADS];
     const int b = blockIdx.x, h = blockIdx.y;
     const int R = a.R, cols = SCAN_THREADS / R;
     const int part = threadIdx.x % R, cl = threadIdx.x / R;
@@ -173,25 +174,79 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanArgs
         S[i] = (live && row < D) ? sp[row] : 0.f;
     }
 
+    // The next chunk's q, k, v rows, decays and gates travel into registers while this chunk is worked on (all
+    // loads of a chunk are issued together: one trip to memory a chunk, hidden behind the arithmetic).  Token tt of
+    // the chunk: thread i takes elements i and i + 128 of its k and q rows; every load is unconditional, from an
+    // index clamped into the chunk, so that nothing keeps the compiler from issuing them all before the first is
+    // used; what lies outside is never stored.
+    constexpr int NV = CH * 32 / SCAN_THREADS;
+    const T* Kp = reinterpret_cast<const T*>(a.k) + (long)kvh * D;
+    const T* Qp = reinterpret_cast<const T*>(a.q) + (long)kvh * D;
+    const T* Vp = reinterpret_cast<const T*>(a.v) + (long)h * V + col0;
+    T kr[2 * CH], qr[2 * CH], vr[NV];
+    float gr = 0.f, br = 1.f;
+    const bool wide = DP > SCAN_THREADS;                       // rows of more than 128 elements: a second half
+    const int i0 = min((int)threadIdx.x, D - 1), i1 = min((int)threadIdx.x + SCAN_THREADS, D - 1);
+    const int cshift = 31 - __clz(cols);                       // cols is a power of two
+    auto fetch = [&](int c0, int nt) {
+#pragma unroll
+        for (int tt = 0; tt < CH; ++tt) {
+            const long t = c0 + min(tt, nt - 1);
+            kr[tt] = __ldg(Kp + t * a.ldk + i0);
+            qr[tt] = __ldg(Qp + t * a.ldq + i0);
+        }
+        if (wide) {
+#pragma unroll
+            for (int tt = 0; tt < CH; ++tt) {
+                const long t = c0 + min(tt, nt - 1);
+                kr[CH + tt] = __ldg(Kp + t * a.ldk + i1);
+                qr[CH + tt] = __ldg(Qp + t * a.ldq + i1);
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < NV; ++e) {
+            const int idx = min((int)threadIdx.x + e * SCAN_THREADS, nt * cols - 1);
+            const int tt = idx >> cshift, c = min(idx - (tt << cshift), V - 1 - col0);
+            vr[e] = __ldg(Vp + (long)(c0 + tt) * a.ldv + c);
+        }
+        const long t = c0 + min((int)threadIdx.x, nt - 1);
+        gr = __ldg(a.g + t * a.g_ld + h);
+        if (DELTA) br = __ldg(a.beta + t * a.H + h);
+    };
+    auto widen = [&](T x) { const float f = to_f32(x); return a.act ? silu_f(f) : f; };
+    auto stash = [&](int nt) {
+        const int i = threadIdx.x;
+        if (i < DP) {
+#pragma unroll
+            for (int tt = 0; tt < CH; ++tt) {
+                k_s[tt][i] = i < D ? widen(kr[tt]) : 0.f;
+                q_s[tt][i] = i < D ? widen(qr[tt]) : 0.f;
+            }
+        }
+        if (wide && i + SCAN_THREADS < DP) {
+#pragma unroll
+            for (int tt = 0; tt < CH; ++tt) {
+                k_s[tt][i + SCAN_THREADS] = i + SCAN_THREADS < D ? widen(kr[CH + tt]) : 0.f;
+                q_s[tt][i + SCAN_THREADS] = i + SCAN_THREADS < D ? widen(qr[CH + tt]) : 0.f;
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < NV; ++e) {
+            const int idx = threadIdx.x + e * SCAN_THREADS;
+            if (idx < nt * cols) {
+                const int tt = idx >> cshift, c = idx - (tt << cshift);
+                v_s[tt][c] = col0 + c < V ? widen(vr[e]) : 0.f;
+            }
+        }
+        if (threadIdx.x < nt) { g_s[threadIdx.x] = gr; b_s[threadIdx.x] = br; }
+    };
+    fetch(r0, min(CH, r1 - r0));
     for (int c0 = r0; c0 < r1; c0 += CH) {
         const int nt = min(CH, r1 - c0);
+        __syncthreads();             // the chunk before is done with the staged rows
+        stash(nt);
         __syncthreads();
-        for (int idx = threadIdx.x; idx < nt * DP; idx += SCAN_THREADS) {
-            const int tt = idx / DP, i = idx - tt * DP;
-            const long t = c0 + tt;
-            k_s[tt][i] = i < D ? load_act<T>(a.k, t * a.ldk + (long)kvh * D + i, a.act) : 0.f;
-            q_s[tt][i] = i < D ? load_act<T>(a.q, t * a.ldq + (long)kvh * D + i, a.act) : 0.f;
-        }
-        for (int idx = threadIdx.x; idx < nt * cols; idx += SCAN_THREADS) {
-            const int tt = idx / cols, c = idx - tt * cols;
-            v_s[tt][c] = col0 + c < V ? load_act<T>(a.v, (long)(c0 + tt) * a.ldv + (long)h * V + col0 + c, a.act) : 0.f;
-        }
-        if (threadIdx.x < nt) {
-            const long t = c0 + threadIdx.x;
-            g_s[threadIdx.x] = a.g[t * a.g_ld + h];
-            b_s[threadIdx.x] = DELTA ? a.beta[t * a.H + h] : 1.f;
-        }
-        __syncthreads();
+        if (c0 + CH < r1) fetch(c0 + CH, min(CH, r1 - c0 - CH));
         for (int tt = 0; tt < nt; ++tt) {
             const float gt = g_s[tt];
             float u = v_s[tt][cl];
@@ -225,9 +280,21 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanArgs
                 r0s = fmaf(S[i], qq.x, r0s); r1s = fmaf(S[i + 1], qq.y, r1s);
                 r2s = fmaf(S[i + 2], qq.z, r2s); r3s = fmaf(S[i + 3], qq.w, r3s);
             }
-            float rd = (r0s + r1s) + (r2s + r3s);
-            for (int o = R >> 1; o > 0; o >>= 1) rd += __shfl_xor_sync(0xffffffffu, rd, o);
-            if (live && part == 0) a.out[(long)(c0 + tt) * a.ldo + (long)h * V + col] = rd;
+            // this lane's share of the read-out; the lanes' shares are added up after the chunk, eight tokens'
+            // reductions side by side, instead of one chain of shuffles in every token's way
+            rd_s[tt][threadIdx.x] = (r0s + r1s) + (r2s + r3s);
+        }
+        float rd[CH];
+#pragma unroll
+        for (int tt = 0; tt < CH; ++tt) rd[tt] = rd_s[tt][threadIdx.x];     // (its own writes)
+        for (int o = R >> 1; o > 0; o >>= 1) {
+#pragma unroll
+            for (int tt = 0; tt < CH; ++tt) rd[tt] += __shfl_xor_sync(0xffffffffu, rd[tt], o);
+        }
+        if (live && part == 0) {
+#pragma unroll
+            for (int tt = 0; tt < CH; ++tt)
+                if (tt < nt) a.out[(long)(c0 + tt) * a.ldo + (long)h * V + col] = rd[tt];
         }
     }
     if (live) {
@@ -334,6 +401,12 @@ extern "C" int fx_state_scan(const void* q, long ldq, const void* k, long ldk, c
     // lanes per column: at least 4, and enough for at most 32 rows a lane; rows a lane in steps of 4
     int R = 4;
     while ((D + R - 1) / R > 32) R *= 2;
+    // Few requests leave most schedulers without a warp, and a warp alone issues an instruction every four cycles
+    // (each waits for the one before): columns are then shared by more lanes (up to 16, at least 4 rows each), which
+    // shortens every warp's chain and makes more warps, until there are two for every scheduler.  Only the grouping
+    // of a dot product's partial sums depends on it.
+    auto warps = [&](int r) { return (long)n_entries * H * fx_cdiv(V, SCAN_THREADS / r) * (SCAN_THREADS / 32); };
+    while (R < 16 && (D + 2 * R - 1) / (2 * R) >= 4 && warps(R) < 2L * 4 * fx_sm_count()) R *= 2;
     const int rpl = (((D + R - 1) / R) + 3) & ~3;
     ScanArgs a;
     a.q = q; a.k = k; a.v = v; a.ldq = ldq; a.ldk = ldk; a.ldv = ldv; a.dtype = dtype; a.act = act;

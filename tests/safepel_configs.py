@@ -49,7 +49,24 @@ SAFEPEL_C = {
     ],
 }
 
-CONFIGS = {"A": (SAFEPEL_A, 11), "B": (SAFEPEL_B, 12), "C": (SAFEPEL_C, 13)}
+# D: delta layers only (no layer keeps pages: the cache manager has no page group at all), q/k heads of 130 rows
+# (more than 128: the recurrence kernel's wide form), an odd number of value columns.
+SAFEPEL_D = {
+    "architecture": ARCH, "vocab": 61, "width": 40, "norm": {"eps": 1e-6}, "logit_scale": 0.3,
+    "layers": [delta(2, 1, 130, 9, 4, 64), delta(1, 1, 6, 70, 5, None)],
+}
+
+# E: parallel layers only, as many key heads as query heads, a head size that is no multiple of 8, a window longer
+# than anything the tests feed, a rotary width of 2.
+SAFEPEL_E = {
+    "architecture": ARCH, "vocab": 73, "width": 48, "norm": {"eps": 1e-5}, "logit_scale": 1.5,
+    "layers": [
+        parallel(3, 3, 20, 500, 2, 77.0, 0.4, 2.5, 4, 12, 5, [0.9, 0.8, 0.7, 0.6], 0.9, 0.2, 72),
+        parallel(2, 1, 36, 33, 36, 10000.0, 0.2, 50.0, 1, 24, 48, [0.98], 0.5, 1.0, None),
+    ],
+}
+
+CONFIGS = {"A": (SAFEPEL_A, 11), "B": (SAFEPEL_B, 12), "C": (SAFEPEL_C, 13), "D": (SAFEPEL_D, 14), "E": (SAFEPEL_E, 15)}
 
 
 def make_folder(tmp_path, name, std=0.15):

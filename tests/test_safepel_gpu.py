@@ -421,3 +421,21 @@ def test_trace_replay_of_a_safepel_folder(folders, tmp_path):
     s0 = torch.from_numpy(np.fromfile(out / "0.f32", dtype="<f4").reshape(2, -1))
     s2 = torch.from_numpy(np.fromfile(out / "2.f32", dtype="<f4").reshape(2, -1))
     assert rel(s0, want[[0, 4]]) < 5e-5 and rel(s2, want[[7, 1]]) < 5e-5
+
+
+def test_command_line_generates_with_a_safepel_folder(folders):
+    import os
+    import subprocess
+    import sys
+
+    import plain_qwen2moe as reader
+
+    cfg, w = reader.load_model(folders["C"], torch.float32)
+    prompt = [5, 9, 20, 31]
+    want = ps.greedy(cfg, w, prompt, 6)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "ferrox"), "-m", folders["C"], "--tokens", "5,9,20,31",
+                        "-n", "6", "--temp", "0", "--dtype", "float32", "--ignore-eos", "--repeat-penalty", "1.0"], capture_output=True, text=True,
+                       timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [int(t) for t in r.stdout.split()] == want
