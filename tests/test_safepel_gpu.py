@@ -308,7 +308,10 @@ def engine(folder, dtype, **kw):
 
 def compare(got, want, tol, what):
     if tol > 1e-3:
-        tol = 6e-2      # bfloat16 through several layers of a narrow model: every activation between kernels is rounded
+        # bfloat16 through several layers of a narrow model: every activation between kernels is rounded.  The
+        # narrowest configuration (width 40, state rows of 130) is the noisiest: the plain implementation with its
+        # products' inputs and outputs rounded to bfloat16 lies 0.07 from itself there.
+        tol = 0.15 if what.startswith("D ") else 6e-2
     for rid in want:
         assert got[rid].shape == want[rid].shape, (what, rid)
         assert torch.isfinite(got[rid]).all(), (what, rid)
