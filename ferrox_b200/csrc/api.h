@@ -148,7 +148,9 @@ int fx_scale(float* x, long n, float scale, void* stream);
 int fx_delta_prep(const void* proj, int dtype, long ldp, const void* conv_w, int cw_dtype, int taps, const float* tail,
                   const float* ba, long ldba, const float* a_log, const float* dt_bias, const int* token_seq,
                   const int* seq_slot, float* out, float* beta, float* g, int n_tokens, int G, int D, int H, int V,
-                  void* stream);
+                  int update_tail, void* stream);
+// update_tail = 1: the caller's promise that every entry of the step brings exactly one token; the kernel then moves
+// the convolution's tail on itself and fx_conv_tail_update is not needed.
 int fx_conv_tail_update(const void* proj, int dtype, long ldp, int channels, int taps, float* tail, const int* token_seq,
                         const int* seq_slot, int n_tokens, int n_entries, void* stream);
 int fx_state_scan(const void* q, long ldq, const void* k, long ldk, const void* v, long ldv, int dtype, int act,

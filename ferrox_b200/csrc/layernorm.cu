@@ -12,7 +12,7 @@
 
 namespace {
 
-constexpr int LN_THREADS = 256;
+constexpr int LN_THREADS = 1024;   // at most; see ln_threads
 
 struct RowStats { float mean, rstd; };
 
@@ -76,6 +76,14 @@ __global__ void scale_kernel(float* __restrict__ x, long n, float s)
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) x[i] *= s;
 }
 
+// Few rows (a decode step) leave the kernel's time to the trips of one block through its row: more threads, fewer.
+inline int ln_threads(int hidden, int n_rows)
+{
+    const int per = n_rows >= 256 ? 8 : 2;      // elements a thread; many rows fill the machine with smaller blocks
+    int n = ((hidden + per - 1) / per + 31) / 32 * 32;
+    return n < 64 ? 64 : (n > LN_THREADS ? LN_THREADS : n);
+}
+
 }  // namespace
 
 extern "C" int fx_layernorm(const float* x, const int* rows, const void* w, int w_dtype, float eps, void* out,
@@ -84,8 +92,8 @@ extern "C" int fx_layernorm(const float* x, const int* rows, const void* w, int 
     if (n_rows <= 0) return FX_OK;
     if (hidden <= 0) return FX_ERR_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
-    if (out_dtype == FX_F32) fx_launch_pdl(layernorm_kernel<float>, n_rows, LN_THREADS, 0, s, x, rows, w, w_dtype, eps, (float*)out, hidden);
-    else if (out_dtype == FX_BF16) fx_launch_pdl(layernorm_kernel<bf16>, n_rows, LN_THREADS, 0, s, x, rows, w, w_dtype, eps, (bf16*)out, hidden);
+    if (out_dtype == FX_F32) fx_launch_pdl(layernorm_kernel<float>, n_rows, ln_threads(hidden, n_rows), 0, s, x, rows, w, w_dtype, eps, (float*)out, hidden);
+    else if (out_dtype == FX_BF16) fx_launch_pdl(layernorm_kernel<bf16>, n_rows, ln_threads(hidden, n_rows), 0, s, x, rows, w, w_dtype, eps, (bf16*)out, hidden);
     else return FX_ERR_DTYPE;
     return fx_launch_status();
 }
@@ -99,10 +107,10 @@ extern "C" int fx_layernorm_residual(float* h, const void* y1, int y1_dtype, flo
     if (hidden <= 0 || !y1 || !w_post || (w_next && !x_out)) return FX_ERR_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     if (!w_next || x_dtype == FX_F32)
-        fx_launch_pdl(layernorm_residual_kernel<float>, n_rows, LN_THREADS, 0, s, h, y1, y1_dtype, s1, y2, y2_dtype, s2,
+        fx_launch_pdl(layernorm_residual_kernel<float>, n_rows, ln_threads(hidden, n_rows), 0, s, h, y1, y1_dtype, s1, y2, y2_dtype, s2,
                       w_post, wp_dtype, eps, w_next, wn_dtype, eps_next, (float*)x_out, hidden);
     else if (x_dtype == FX_BF16)
-        fx_launch_pdl(layernorm_residual_kernel<bf16>, n_rows, LN_THREADS, 0, s, h, y1, y1_dtype, s1, y2, y2_dtype, s2,
+        fx_launch_pdl(layernorm_residual_kernel<bf16>, n_rows, ln_threads(hidden, n_rows), 0, s, h, y1, y1_dtype, s1, y2, y2_dtype, s2,
                       w_post, wp_dtype, eps, w_next, wn_dtype, eps_next, (bf16*)x_out, hidden);
     else return FX_ERR_DTYPE;
     return fx_launch_status();

@@ -36,7 +36,7 @@ __device__ __forceinline__ int first_row_of(const int* __restrict__ token_seq, i
 }
 
 // ------------------------------------------------------------------------------------------------------------
-// Gated delta rule, what comes before the recurrence.  One block per token.
+// Gated delta rule, what comes before the recurrence.
 //   proj row: [ q (G*D) | k (G*D) | v (H*V) | ... ]  as projected
 //   conv: y[c] = sum_j w[c, j] x_{t - (taps-1-j)}[c]; inputs before the step come from tail[slot] ([taps-1][C],
 //   oldest first; zeros at the start of a request)
@@ -44,22 +44,29 @@ __device__ __forceinline__ int first_row_of(const int* __restrict__ token_seq, i
 //   beta = sigmoid(b), g = exp(-exp(A_log) softplus(a + dt_bias))   from ba = [ b (H) | a (H) ] (32-bit)
 constexpr int MAX_TAPS = 16;
 
+constexpr int PREP_THREADS = 256;
+
+// Grid (tokens, units): unit u < 2G is one q or k head (convolution, SiLU, unit length); the units after them are
+// slices of PREP_THREADS value channels; unit 0 also makes the token's gates.
 template <typename T>
-__global__ void __launch_bounds__(256) delta_prep_kernel(
+__global__ void __launch_bounds__(PREP_THREADS) delta_prep_kernel(
     const T* __restrict__ proj, long ldp, const void* __restrict__ conv_w, int cw_dtype, int taps,
-    const float* __restrict__ tail, const float* __restrict__ ba, long ldba, const float* __restrict__ a_log,
+    const float* tail, const float* __restrict__ ba, long ldba, const float* __restrict__ a_log,
     const float* __restrict__ dt_bias, const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
-    float* __restrict__ out, float* __restrict__ beta, float* __restrict__ g, int G, int D, int H, int V)
+    float* __restrict__ out, float* __restrict__ beta, float* __restrict__ g, int G, int D, int H, int V,
+    float* tail_new)
 {
-    extern __shared__ float row_s[];   // C floats
-    const int t = blockIdx.x;
+    extern __shared__ float row_s[];   // D floats
+    __shared__ float scratch[33];
+    fx_pdl_wait();
+    const int t = blockIdx.x, u = blockIdx.y;
     const int C = 2 * G * D + H * V;
     const int b = token_seq[t];
     // how many rows before t belong to the same entry (at most taps - 1 matter)
     int own = 0;
     while (own < taps - 1 && t - own - 1 >= 0 && token_seq[t - own - 1] == b) ++own;
     const float* tl = tail + (long)seq_slot[b] * (taps - 1) * C;
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    auto conv = [&](int c) {
         float acc = 0.f;
         for (int j = 0; j < taps; ++j) {
             const int back = taps - 1 - j;          // this tap's input lies `back` tokens before t
@@ -68,30 +75,37 @@ __global__ void __launch_bounds__(256) delta_prep_kernel(
             else x = tl[(long)(taps - 1 - (back - own)) * C + c];
             acc = fmaf(load_any(conv_w, cw_dtype, (long)c * taps + j), x, acc);
         }
-        row_s[c] = silu_f(acc);
-    }
-    __syncthreads();
-    // unit length per q and k head: one warp per head
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
+        // tail_new (the caller's promise that every entry brings exactly one token): this thread is then the only
+        // reader of the channel's tail in the whole step, and moves it on by the token's input itself
+        if (tail_new && taps > 1) {
+            float* tn = tail_new + (long)seq_slot[b] * (taps - 1) * C;
+            for (int j = 0; j + 1 < taps - 1; ++j) tn[(long)j * C + c] = tn[(long)(j + 1) * C + c];
+            tn[(long)(taps - 2) * C + c] = to_f32(proj[(long)t * ldp + c]);
+        }
+        return silu_f(acc);
+    };
     float* o = out + (long)t * C;
-    for (int hd = warp; hd < 2 * G; hd += nwarp) {
-        const float* x = row_s + hd * D;
+    if (u < 2 * G) {
         float ss = 0.f;
-        for (int i = lane; i < D; i += 32) ss = fmaf(x[i], x[i], ss);
-        ss = warp_sum(ss);
+        for (int i = threadIdx.x; i < D; i += blockDim.x) { const float x = conv(u * D + i); row_s[i] = x; ss = fmaf(x, x, ss); }
+        ss = block_sum(ss, scratch);
         float inv = 1.0f / sqrtf(ss + 1e-6f);
-        if (hd < G) inv *= 1.0f / sqrtf((float)D);
-        for (int i = lane; i < D; i += 32) o[hd * D + i] = x[i] * inv;
+        if (u < G) inv *= 1.0f / sqrtf((float)D);
+        for (int i = threadIdx.x; i < D; i += blockDim.x) o[u * D + i] = row_s[i] * inv;   // (its own writes)
+    } else {
+        const int c = 2 * G * D + (u - 2 * G) * PREP_THREADS + threadIdx.x;
+        if (c < C) o[c] = conv(c);
     }
-    for (int c = 2 * G * D + threadIdx.x; c < C; c += blockDim.x) o[c] = row_s[c];
-    for (int hd = threadIdx.x; hd < H; hd += blockDim.x) {
-        const float* r = ba + (long)t * ldba;
-        beta[(long)t * H + hd] = sigmoid_f(r[hd]);
-        // The decay is raised to the power of the distance a memory travels: an error of one unit in its last place
-        // grows a thousandfold over a thousand tokens.  Its three transcendental steps are therefore taken in 64 bits
-        // and rounded once (a handful of values a token).
-        const double sp = log1p(exp((double)(r[H + hd] + dt_bias[hd])));
-        g[(long)t * H + hd] = (float)exp(-exp((double)a_log[hd]) * sp);
+    if (u == 0) {
+        for (int hd = threadIdx.x; hd < H; hd += blockDim.x) {
+            const float* r = ba + (long)t * ldba;
+            beta[(long)t * H + hd] = sigmoid_f(r[hd]);
+            // The decay is raised to the power of the distance a memory travels: an error of one unit in its last
+            // place grows a thousandfold over a thousand tokens.  Its three transcendental steps are therefore taken
+            // in 64 bits and rounded once (a handful of values a token).
+            const double sp = log1p(exp((double)(r[H + hd] + dt_bias[hd])));
+            g[(long)t * H + hd] = (float)exp(-exp((double)a_log[hd]) * sp);
+        }
     }
 }
 
@@ -103,6 +117,7 @@ __global__ void __launch_bounds__(256) conv_tail_update_kernel(
     const T* __restrict__ proj, long ldp, int C, int taps, float* __restrict__ tail,
     const int* __restrict__ token_seq, const int* __restrict__ seq_slot, int n_tokens)
 {
+    fx_pdl_wait();
     const int b = blockIdx.x;
     const int r0 = first_row_of(token_seq, n_tokens, b), r1 = first_row_of(token_seq, n_tokens, b + 1);
     const int n = r1 - r0, keep = taps - 1;
@@ -155,6 +170,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanArgs
     __shared__ float v_s[CH][SCAN_THREADS];
     __shared__ float g_s[CH], b_s[CH];
     __shared__ float rd_s[CH][SCAN_THREADS];
+    fx_pdl_wait();
     const int b = blockIdx.x, h = blockIdx.y;
     const int R = a.R, cols = SCAN_THREADS / R;
     const int part = threadIdx.x % R, cl = threadIdx.x / R;
@@ -311,8 +327,8 @@ void launch_scan(const ScanArgs& a, int n_entries, cudaStream_t s)
 {
     const int cols = SCAN_THREADS / a.R;
     dim3 grid(n_entries, a.H, (unsigned)fx_cdiv(a.V, cols));
-    if (a.beta) state_scan_kernel<RPL, true, T><<<grid, SCAN_THREADS, 0, s>>>(a);
-    else state_scan_kernel<RPL, false, T><<<grid, SCAN_THREADS, 0, s>>>(a);
+    if (a.beta) fx_launch_pdl(state_scan_kernel<RPL, true, T>, grid, SCAN_THREADS, 0, s, a);
+    else fx_launch_pdl(state_scan_kernel<RPL, false, T>, grid, SCAN_THREADS, 0, s, a);
 }
 
 template <typename T>
@@ -340,6 +356,7 @@ __global__ void __launch_bounds__(128) gated_group_norm_kernel(
     float eps, int act, OT* __restrict__ out, int groups, int width)
 {
     __shared__ float scratch[33];
+    fx_pdl_wait();
     const int t = blockIdx.x, grp = blockIdx.y;
     const float* xr = x + ((long)t * groups + grp) * width;
     const GT* gr = gate + (long)t * ldg + (long)grp * width;
@@ -359,22 +376,23 @@ __global__ void __launch_bounds__(128) gated_group_norm_kernel(
 extern "C" int fx_delta_prep(const void* proj, int dtype, long ldp, const void* conv_w, int cw_dtype, int taps,
                              const float* tail, const float* ba, long ldba, const float* a_log, const float* dt_bias,
                              const int* token_seq, const int* seq_slot, float* out, float* beta, float* g,
-                             int n_tokens, int G, int D, int H, int V, void* stream)
+                             int n_tokens, int G, int D, int H, int V, int update_tail, void* stream)
 {
     if (n_tokens <= 0) return FX_OK;
-    const long C = 2L * G * D + (long)H * V;
-    if (taps < 1 || taps > MAX_TAPS || G <= 0 || H % G || C * 4 > 200 * 1024) return FX_ERR_SIZE;
+    if (taps < 1 || taps > MAX_TAPS || G <= 0 || H % G || D <= 0 || D > 8192) return FX_ERR_SIZE;
+    float* tail_new = update_tail ? const_cast<float*>(tail) : nullptr;
     cudaStream_t s = (cudaStream_t)stream;
-    const size_t smem = (size_t)C * 4;
-    if (dtype == FX_F32) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(delta_prep_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        delta_prep_kernel<float><<<n_tokens, 256, smem, s>>>((const float*)proj, ldp, conv_w, cw_dtype, taps, tail, ba,
-            ldba, a_log, dt_bias, token_seq, seq_slot, out, beta, g, G, D, H, V);
-    } else if (dtype == FX_BF16) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(delta_prep_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        delta_prep_kernel<bf16><<<n_tokens, 256, smem, s>>>((const bf16*)proj, ldp, conv_w, cw_dtype, taps, tail, ba,
-            ldba, a_log, dt_bias, token_seq, seq_slot, out, beta, g, G, D, H, V);
-    } else return FX_ERR_DTYPE;
+    const size_t smem = (size_t)D * 4;
+    const long units = 2L * G + fx_cdiv((long)H * V, PREP_THREADS);
+    if (units > 65535) return FX_ERR_SIZE;
+    dim3 grid(n_tokens, (unsigned)units);
+    if (dtype == FX_F32)
+        fx_launch_pdl(delta_prep_kernel<float>, grid, PREP_THREADS, smem, s, (const float*)proj, ldp, conv_w, cw_dtype, taps,
+                      tail, ba, ldba, a_log, dt_bias, token_seq, seq_slot, out, beta, g, G, D, H, V, tail_new);
+    else if (dtype == FX_BF16)
+        fx_launch_pdl(delta_prep_kernel<bf16>, grid, PREP_THREADS, smem, s, (const bf16*)proj, ldp, conv_w, cw_dtype, taps,
+                      tail, ba, ldba, a_log, dt_bias, token_seq, seq_slot, out, beta, g, G, D, H, V, tail_new);
+    else return FX_ERR_DTYPE;
     return fx_launch_status();
 }
 
@@ -384,8 +402,8 @@ extern "C" int fx_conv_tail_update(const void* proj, int dtype, long ldp, int ch
     if (n_tokens <= 0 || n_entries <= 0 || taps <= 1) return FX_OK;
     if (taps > MAX_TAPS) return FX_ERR_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == FX_F32) conv_tail_update_kernel<float><<<n_entries, 256, 0, s>>>((const float*)proj, ldp, channels, taps, tail, token_seq, seq_slot, n_tokens);
-    else if (dtype == FX_BF16) conv_tail_update_kernel<bf16><<<n_entries, 256, 0, s>>>((const bf16*)proj, ldp, channels, taps, tail, token_seq, seq_slot, n_tokens);
+    if (dtype == FX_F32) fx_launch_pdl(conv_tail_update_kernel<float>, n_entries, 256, 0, s, (const float*)proj, ldp, channels, taps, tail, token_seq, seq_slot, n_tokens);
+    else if (dtype == FX_BF16) fx_launch_pdl(conv_tail_update_kernel<bf16>, n_entries, 256, 0, s, (const bf16*)proj, ldp, channels, taps, tail, token_seq, seq_slot, n_tokens);
     else return FX_ERR_DTYPE;
     return fx_launch_status();
 }
@@ -427,9 +445,11 @@ extern "C" int fx_gated_group_norm(const float* x, const void* gate, int gate_dt
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(n_tokens, groups);
     if (gate_dtype == FX_F32 && out_dtype == FX_F32)
-        gated_group_norm_kernel<float, float><<<grid, 128, 0, s>>>(x, (const float*)gate, ldg, w, w_dtype, eps, act, (float*)out, groups, width);
+        fx_launch_pdl(gated_group_norm_kernel<float, float>, grid, 128, 0, s, x, (const float*)gate, ldg, w, w_dtype, eps, act, (float*)out, groups, width);
+    else if (gate_dtype == FX_F32 && out_dtype == FX_BF16)
+        fx_launch_pdl(gated_group_norm_kernel<float, bf16>, grid, 128, 0, s, x, (const float*)gate, ldg, w, w_dtype, eps, act, (bf16*)out, groups, width);
     else if (gate_dtype == FX_BF16 && out_dtype == FX_BF16)
-        gated_group_norm_kernel<bf16, bf16><<<grid, 128, 0, s>>>(x, (const bf16*)gate, ldg, w, w_dtype, eps, act, (bf16*)out, groups, width);
+        fx_launch_pdl(gated_group_norm_kernel<bf16, bf16>, grid, 128, 0, s, x, (const bf16*)gate, ldg, w, w_dtype, eps, act, (bf16*)out, groups, width);
     else return FX_ERR_DTYPE;
     return fx_launch_status();
 }

@@ -55,7 +55,7 @@ _SIGNATURES = {
     "fx_layernorm": [_P, _P, _P, _I, _F, _P, _I, _I, _I, _P],
     "fx_layernorm_residual": [_P, _P, _I, _F, _P, _I, _F, _P, _I, _F, _P, _I, _F, _P, _I, _I, _I, _P],
     "fx_scale": [_P, _L, _F, _P],
-    "fx_delta_prep": [_P, _I, _L, _P, _I, _I, _P, _P, _L, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "fx_delta_prep": [_P, _I, _L, _P, _I, _I, _P, _P, _L, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "fx_conv_tail_update": [_P, _I, _L, _I, _I, _P, _P, _P, _I, _I, _P],
     "fx_state_scan": [_P, _L, _P, _L, _P, _L, _I, _I, _P, _L, _P, _P, _P, _L, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "fx_gated_group_norm": [_P, _P, _I, _L, _P, _I, _F, _I, _P, _I, _I, _I, _I, _P],
@@ -337,15 +337,18 @@ def scale_(x, factor, stream=None):
     return x
 
 
-def delta_prep(proj, conv_w, taps, tail, ba, a_log, dt_bias, token_seq, seq_slot, out, beta, g, G, D, H, V, stream=None):
+def delta_prep(proj, conv_w, taps, tail, ba, a_log, dt_bias, token_seq, seq_slot, out, beta, g, G, D, H, V, stream=None,
+               update_tail=False):
     """What the gated delta rule needs before its recurrence, from rows ``proj`` = [q | k | v | ...] as projected:
     short causal convolution (``conv_w`` [channels, taps], the inputs before the step from ``tail`` [slots, taps-1,
     channels]) and SiLU, q and k to unit length per head (q also times D^-1/2), into ``out`` [T, channels] 32-bit;
-    beta = sigmoid(b) and g = exp(-exp(A_log) softplus(a + dt_bias)) from ``ba`` = [b | a] 32-bit rows."""
+    beta = sigmoid(b) and g = exp(-exp(A_log) softplus(a + dt_bias)) from ``ba`` = [b | a] 32-bit rows.
+    ``update_tail``: only when every entry of the step brings exactly one token; the kernel then also moves the
+    tail on, and :func:`conv_tail_update` is not needed."""
     T = proj.shape[0]
     call("fx_delta_prep", _ptr(proj), code(proj), _rows(proj), _ptr(conv_w), code(conv_w), int(taps), _ptr(tail), _ptr(ba),
          _rows(ba), _ptr(a_log), _ptr(dt_bias), _ptr(token_seq), _ptr(seq_slot), _ptr(out), _ptr(beta), _ptr(g), T, G, D, H, V,
-         stream if stream is not None else stream_ptr())
+         int(update_tail), stream if stream is not None else stream_ptr())
 
 
 def conv_tail_update(proj, channels, taps, tail, token_seq, seq_slot, n_entries, stream=None):

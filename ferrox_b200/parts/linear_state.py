@@ -75,8 +75,9 @@ class GatedDeltaRule(_StateMixer):
     def load(self, src, rt):
         super().load(src, rt)
         p = self.spec.prefix
-        self.w_in = _cat_rows([src.get(p + n) for n in ("q", "k", "v", "g")])          # rows [q | k | v | gate]
-        self.w_ba = _cat_rows([src.get(p + "b"), src.get(p + "a")])                    # rows [b | a]
+        # one product for everything the mixer reads from its input: rows [q | k | v | gate | b | a]; its output is
+        # written in 32 bits, because b and a feed the gates of the recurrence
+        self.w_in = _cat_rows([src.get(p + n) for n in ("q", "k", "v", "g", "b", "a")])
         self.conv_w = torch.cat([src.get(p + n + ".conv").float() for n in ("q", "k", "v")], dim=0).contiguous()
         self.a_log = src.get(p + "A_log").float().contiguous()
         self.dt_bias = src.get(p + "dt_bias").float().contiguous()
@@ -87,22 +88,23 @@ class GatedDeltaRule(_StateMixer):
         s, rt = self.spec, self.rt
         T, H, G, D, V = x.shape[0], s.n_heads, s.n_kv_heads, s.head_dim, s.value_dim
         f32 = torch.float32
-        proj = rt.empty(T, self.channels + self.vv)
+        proj = rt.empty(T, self.channels + self.vv + 2 * H, dtype=f32)
         ops.linear(x, self.w_in, proj, status=batch.status, stream=batch.stream)
-        ba = rt.empty(T, 2 * H, dtype=f32)                     # the gates' inputs stay 32-bit
-        ops.linear(x, self.w_ba, ba, status=batch.status, stream=batch.stream)
+        ba = proj[:, self.channels + self.vv:]
         qkv = rt.empty(T, self.channels, dtype=f32)
         beta, g = rt.empty(T, H, dtype=f32), rt.empty(T, H, dtype=f32)
         tail, state = cache.states["conv_tail"], cache.states["matrix"]
+        single = batch.max_new == 1      # a decode step: the kernel that reads a channel's tail also moves it on
         ops.delta_prep(proj, self.conv_w, s.conv_taps, tail, ba, self.a_log, self.dt_bias, batch.token_seq,
-                       batch.seq_slot, qkv, beta, g, G, D, H, V, stream=batch.stream)
-        ops.conv_tail_update(proj, self.channels, s.conv_taps, tail, batch.token_seq, batch.seq_slot, batch.n_seqs,
-                             stream=batch.stream)
+                       batch.seq_slot, qkv, beta, g, G, D, H, V, stream=batch.stream, update_tail=single)
+        if not single:
+            ops.conv_tail_update(proj, self.channels, s.conv_taps, tail, batch.token_seq, batch.seq_slot, batch.n_seqs,
+                                 stream=batch.stream)
         read = rt.empty(T, self.vv, dtype=f32)
         ops.state_scan(qkv[:, :self.qk], qkv[:, self.qk:2 * self.qk], qkv[:, 2 * self.qk:], g, H, beta, state, read,
                        batch.token_seq, batch.seq_slot, batch.n_seqs, H, G, D, V, stream=batch.stream)
         y = rt.empty(T, self.vv)
-        ops.gated_group_norm(read, proj[:, self.channels:], self.norm_w, s.norm_eps, "silu", y, H, V, stream=batch.stream)
+        ops.gated_group_norm(read, proj[:, self.channels:self.channels + self.vv], self.norm_w, s.norm_eps, "silu", y, H, V, stream=batch.stream)
         ops.linear(y, self.w_o, out, accumulate=accumulate, status=batch.status, stream=batch.stream)
 
 
