@@ -156,6 +156,7 @@ int fx_conv_tail_update(const void* proj, int dtype, long ldp, int channels, int
 int fx_state_scan(const void* q, long ldq, const void* k, long ldk, const void* v, long ldv, int dtype, int act,
                   const float* g, long g_ld, const float* beta, float* state, float* out, long ldo, const int* token_seq,
                   const int* seq_slot, int n_tokens, int n_entries, int H, int G, int D, int V, void* stream);
+int fx_set_scan_lanes(int lanes);   // lanes that share a state column, fixed for measurements (0: the launcher's choice)
 int fx_gated_group_norm(const float* x, const void* gate, int gate_dtype, long ldg, const void* w, int w_dtype, float eps,
                         int act, void* out, int out_dtype, int n_tokens, int groups, int width, void* stream);
 

@@ -322,6 +322,8 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanArgs
     }
 }
 
+int g_scan_lanes = 0;
+
 template <int RPL, typename T>
 void launch_scan(const ScanArgs& a, int n_entries, cudaStream_t s)
 {
@@ -408,6 +410,14 @@ extern "C" int fx_conv_tail_update(const void* proj, int dtype, long ldp, int ch
     return fx_launch_status();
 }
 
+// Lanes that share a state column, fixed for measurements (0: chosen by the launcher); returns the old setting.
+extern "C" int fx_set_scan_lanes(int lanes)
+{
+    const int was = g_scan_lanes;
+    g_scan_lanes = lanes;
+    return was;
+}
+
 // beta null: plain decay (g_ld may be 0: g holds one decay per head); else the delta rule.
 extern "C" int fx_state_scan(const void* q, long ldq, const void* k, long ldk, const void* v, long ldv, int dtype, int act,
                              const float* g, long g_ld, const float* beta, float* state, float* out, long ldo,
@@ -421,10 +431,15 @@ extern "C" int fx_state_scan(const void* q, long ldq, const void* k, long ldk, c
     while ((D + R - 1) / R > 32) R *= 2;
     // Few requests leave most schedulers without a warp, and a warp alone issues an instruction every four cycles
     // (each waits for the one before): columns are then shared by more lanes (up to 16, at least 4 rows each), which
-    // shortens every warp's chain and makes more warps, until there are two for every scheduler.  Only the grouping
-    // of a dot product's partial sums depends on it.
+    // shortens every warp's chain and makes more warps, until there are three for every two schedulers (measured on a
+    // B200, 16 heads of 128 x 128: one prompt of 2,048 tokens 1.2 ms a layer with 4 lanes, 0.95 with 8, 0.91 with 16;
+    // four prompts of 512 tokens 0.37 ms with 4 lanes, 0.5 with 8).  Only the grouping of a dot product's partial
+    // sums depends on it.
     auto warps = [&](int r) { return (long)n_entries * H * fx_cdiv(V, SCAN_THREADS / r) * (SCAN_THREADS / 32); };
-    while (R < 16 && (D + 2 * R - 1) / (2 * R) >= 4 && warps(R) < 2L * 4 * fx_sm_count()) R *= 2;
+    while (R < 16 && (D + 2 * R - 1) / (2 * R) >= 4 && warps(R) < 6L * fx_sm_count()) R *= 2;
+    if (g_scan_lanes >= 4 && g_scan_lanes <= 32 && (D + g_scan_lanes - 1) / g_scan_lanes <= 32 &&
+        (D + g_scan_lanes - 1) / g_scan_lanes >= 1 && (g_scan_lanes & (g_scan_lanes - 1)) == 0)
+        R = g_scan_lanes;
     const int rpl = (((D + R - 1) / R) + 3) & ~3;
     ScanArgs a;
     a.q = q; a.k = k; a.v = v; a.ldq = ldq; a.ldk = ldk; a.ldv = ldv; a.dtype = dtype; a.act = act;

@@ -34,6 +34,7 @@ class KernelError(RuntimeError):
 _P, _I, _L, _F = c_void_p, c_int, c_long, c_float
 _SIGNATURES = {
     "fx_set_pdl": [_I],
+    "fx_set_scan_lanes": [_I],
     "fx_gemm": [_P, _I, _L, _P, _P, _I, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _P, _I, _L, _P],
     "fx_embed": [_P, _I, _P, _P, _I, _I, _I, _P, _P],
     "fx_rmsnorm": [_P, _P, _P, _I, _F, _P, _I, _I, _I, _P],
