@@ -442,3 +442,53 @@ def test_command_line_generates_with_a_safepel_folder(folders):
                        timeout=600)
     assert r.returncode == 0, r.stderr[-2000:]
     assert [int(t) for t in r.stdout.split()] == want
+
+
+def test_preemption_decoding_ahead_and_sampling_with_state_mixers(folders):
+    """A request that is preempted gives its pages AND its state slot back and is recomputed from its tokens; greedy
+    decode steps are replayed graphs issued one ahead of the host; sampled generation is seeded."""
+    import plain_qwen2moe as reader
+
+    cfg, w = reader.load_model(folders["B"], torch.float32)
+    prompts = [[i + 1, i + 3, i + 7, 90, 4, 8, 15, 16] for i in range(4)]
+    want = [ps.greedy(cfg, w, p, 20) for p in prompts]
+    small = engine(folders["B"], "float32", page_size=4, n_pages=14, max_slots=4)     # 4 x 28 positions do not fit 56
+    outs, stats = small.generate(prompts, max_new_tokens=20, return_stats=True)
+    assert stats["preemptions"] >= 1 and outs == want
+    small.cache.check_invariants()
+    roomy = engine(folders["B"], "float32", n_pages=64)
+    outs, stats = roomy.generate(prompts, max_new_tokens=20, return_stats=True)
+    assert outs == want and stats["ahead_steps"] >= 8 and stats["preemptions"] == 0
+    a = roomy.generate([prompts[0]], max_new_tokens=16, temperature=0.9, top_k=20, seed=5)[0]
+    b = roomy.generate([prompts[0]], max_new_tokens=16, temperature=0.9, top_k=20, seed=5)[0]
+    c = roomy.generate([prompts[0]], max_new_tokens=16, temperature=0.9, top_k=20, seed=6)[0]
+    both = roomy.generate([prompts[0], prompts[1]], max_new_tokens=16, temperature=0.9, top_k=20, seed=5)
+    assert a == b and a != c and both[0] == a
+    assert roomy.cache.n_free_slots == 4
+
+
+@pytest.mark.parametrize("dtype", list(DTYPES))
+def test_gated_delta_rule_keeps_an_early_token_when_its_decay_is_near_one(dtype):
+    """A_log far below zero: g stays within a thousandth of 1, so a token made large at the start is still read
+    hundreds of tokens later (and with the decay a little off it would be read differently)."""
+    from ferrox_b200.parts.specs import GatedDeltaSpec
+
+    dt, tol = DTYPES[dtype]
+    hidden, H, G, D, V = 64, 2, 1, 32, 16
+    spec = GatedDeltaSpec(hidden=hidden, n_heads=H, n_kv_heads=G, head_dim=D, value_dim=V, conv_taps=4, norm_eps=1e-6, prefix="d.")
+    w = random_tensors(spec, seed=9, std=0.3)
+    w["d.A_log"] = torch.full((H,), -7.0).to(torch.bfloat16)
+    part, rt = load_part(spec, w, dt)
+    g = torch.Generator().manual_seed(3)
+    xs = [torch.randn(n, hidden, generator=g) for n in (400, 30)]
+    xs[0][1] *= 20.0
+    xs = [x.to(dt).float() for x in xs]
+    m = dict(heads=H, kv_heads=G, dim=D, vdim=V)
+    wf = {k: v.float() for k, v in w.items()}
+    want = [ps.delta_mixer(x, wf, "d.", m, 1e-6) for x in xs]
+    quiet = xs[0].clone()
+    quiet[1] /= 20.0
+    assert rel(ps.delta_mixer(quiet, wf, "d.", m, 1e-6)[350:], want[0][350:]) > 0.05      # the test can tell
+    got = run_in_cuts(MixerHarness(part, rt, hidden, max_positions=1024), xs, CUTS["prompt then decode"])
+    for a, b in zip(got, want):
+        assert rel(a, b) < tol
