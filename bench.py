@@ -165,7 +165,7 @@ def safepel_shape(width, layers, ff, vocab=32768, window=1024):
              "mlp": {"kind": "dense", "ff": ff}}
     par = {"type": "parallel", "mlp": {"kind": "dense", "ff": ff}, "mixer": {
         "left": {"heads": h, "kv_heads": max(1, h // 4), "dim": 128, "vdim": 128, "mask": {"size": window},
-                 "rot": {"dims": 64, "base": 500000.0}, "scale": 128 ** -0.5, "softcap": 30.0},
+                 "rot": {"dims": 64, "base": 1000000.0}, "scale": 128 ** -0.5, "softcap": 30.0},
         "right": {"heads": h, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** -(3 + 8 * i / max(1, h - 1)) for i in range(h)]},
         "left_scale": 1.0, "right_scale": 1.0}}
     return {"architecture": "Safepel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "logit_scale": 1.0,
