@@ -57,16 +57,28 @@ SAFEPEL_D = {
 }
 
 # E: parallel layers only, as many key heads as query heads, a head size that is no multiple of 8, a window longer
-# than anything the tests feed, a rotary width of 2.
+# than anything the tests feed, a rotary width of 2, a width and a feed-forward that are no multiple of 8.
 SAFEPEL_E = {
-    "architecture": ARCH, "vocab": 73, "width": 48, "norm": {"eps": 1e-5}, "logit_scale": 1.5,
+    "architecture": ARCH, "vocab": 73, "width": 44, "norm": {"eps": 1e-5}, "logit_scale": 1.5,
     "layers": [
-        parallel(3, 3, 20, 500, 2, 77.0, 0.4, 2.5, 4, 12, 5, [0.9, 0.8, 0.7, 0.6], 0.9, 0.2, 72),
+        parallel(3, 3, 20, 500, 2, 77.0, 0.4, 2.5, 4, 12, 5, [0.9, 0.8, 0.7, 0.6], 0.9, 0.2, 70),
         parallel(2, 1, 36, 33, 36, 10000.0, 0.2, 50.0, 1, 24, 48, [0.98], 0.5, 1.0, None),
     ],
 }
 
-CONFIGS = {"A": (SAFEPEL_A, 11), "B": (SAFEPEL_B, 12), "C": (SAFEPEL_C, 13), "D": (SAFEPEL_D, 14), "E": (SAFEPEL_E, 15)}
+# F: attention heads of 64 and of 128 (the sizes the kernels that stream pages by TMA and the tcgen05 prompt kernel
+# take when scores are not capped), windows that cross the 64-key blocks, state heads of 64 and 128 rows.
+SAFEPEL_F = {
+    "architecture": ARCH, "vocab": 131, "width": 128, "norm": {"eps": 1e-6}, "logit_scale": 0.7,
+    "layers": [
+        parallel(4, 1, 64, 70, 64, 10000.0, 0.125, 15.0, 2, 64, 32, [0.9, 0.99], 1.0, 0.5, 192),
+        delta(2, 1, 128, 64, 4, 192),
+        parallel(2, 2, 128, 65, 32, 500.0, 0.09, 25.0, 1, 128, 128, [0.95], 0.6, 1.2, None),
+    ],
+}
+
+CONFIGS = {"A": (SAFEPEL_A, 11), "B": (SAFEPEL_B, 12), "C": (SAFEPEL_C, 13), "D": (SAFEPEL_D, 14), "E": (SAFEPEL_E, 15),
+           "F": (SAFEPEL_F, 16)}
 
 
 def make_folder(tmp_path, name, std=0.15):

@@ -300,7 +300,7 @@ def expected(folders):
 def engine(folder, dtype, **kw):
     from ferrox_b200 import Engine
 
-    kw.setdefault("page_size", 8)
+    kw.setdefault("page_size", 64 if folder.endswith("_F") else 8)     # F: the page size of serving
     kw.setdefault("n_pages", 48)
     kw.setdefault("max_slots", 4)
     return Engine.from_folder(folder, dtype=dtype, **kw)
