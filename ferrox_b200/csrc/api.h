@@ -24,7 +24,8 @@ int fx_rmsnorm(const float* x, const int* rows, const void* w, int w_dtype, floa
 int fx_silu_mul(const void* gu, long ld_in, void* out, long ld_out, int dtype, const int* n_rows_dev, int rows, int n,
                 void* stream);
 int fx_glu_mul(const void* gu, long ld_in, void* out, long ld_out, int dtype, const int* n_rows_dev, int rows, int n,
-               int act, void* stream);   // act(gate) * up; act 0: SiLU, 1: ReLU
+               int act, float act_limit, float act_alpha, void* stream);   // act 0: SiLU(gate) * up, 1: ReLU(gate) * up,
+                                                                          // 2: the clamped unit (fx_clamped_glu)
 int fx_rope_kv_write(void* qkv, int dtype, long ld, const int* positions, const int* token_seq, const int* seq_slot,
                      const float* inv_freq, const float* cos_sin, int rotary_dim, int pairing, void* k_pages, void* v_pages, const int* block_table,
                      int table_width, int page_size, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
@@ -38,6 +39,14 @@ int fx_paged_attention(const void* q, long ldq, const void* k_pages, const void*
                        const int* block_table, int table_width, int page_size, const int* positions,
                        const int* token_seq, const int* seq_slot, void* out, long ldo, int n_tokens, int n_heads,
                        int n_kv_heads, int head_dim, int window, float scale, float softcap, void* stream);
+
+// fx_paged_attention with keys and values of different widths and strides, strided queries and outputs, and an
+// optional distance bias slopes[h] * (i - j) taken off the scores (attention_generic.cu)
+int fx_paged_attention_ex(const void* q, long ldq, long ldqh, const void* k_pages, const void* v_pages, long ldk, long ldv,
+                          int dtype, const int* block_table, int table_width, int page_size, const int* positions,
+                          const int* token_seq, const int* seq_slot, void* out, long ldo, long ldoh, int n_tokens,
+                          int n_heads, int n_kv_heads, int key_dim, int value_dim, int window, float scale, float softcap,
+                          const float* slopes, void* stream);
 
 int fx_prefill_attention_tc(const void* q, long ldq, int n_tokens, const void* k_pages, const void* v_pages, int n_pages,
                             const int* block_table, int table_width, int page_size, const int* items, int n_items,
@@ -56,19 +65,23 @@ int fx_moe_align(const int* ids, int n_tokens, int top_k, int n_experts, int* sc
 
 int fx_gemm_tc(const void* X, long ldx, const void* W, long ldw, long w_group_stride, int w_rows, const void* bias,
                int bias_dtype, void* C, int c_dtype, long ldc, int accumulate, int M, int N, int K, int gated,
-               int gate_up_offset, const int* group_offsets, int n_groups, int* status, void* stream);
+               int gate_up_offset, float act_limit, float act_alpha, const int* group_offsets, int n_groups, int* status,
+               void* stream);
 int fx_gemm_tc_swap(const void* X, long ldx, const void* W, long ldw, long w_group_stride, int w_rows, const void* bias,
                     int bias_dtype, void* C, int c_dtype, long ldc, int accumulate, int M, int N, int K, int gated,
-                    int gate_up_offset, const int* group_offsets, int n_groups, int tokens_per_tile, int weights_first,
+                    int gate_up_offset, float act_limit, float act_alpha, const int* group_offsets, int n_groups, int tokens_per_tile, int weights_first,
                     int k_splits, float* partials, int* status, void* stream);
 int fx_gemm_tc2(const void* X, long ldx, const void* W, long ldw, int w_rows, const void* bias, int bias_dtype, void* C,
-                int c_dtype, long ldc, int accumulate, int M, int N, int K, int gated, int gate_up_offset, int* status,
-                void* stream);
+                int c_dtype, long ldc, int accumulate, int M, int N, int K, int gated, int gate_up_offset, float act_limit,
+                float act_alpha, int* status, void* stream);
 int fx_moe_combine_norm(float* h, const void* y, int dtype, const int* inv_perm, const float* topk_w, int top_k,
                         const void* shared, const float* shared_gate_logit, long gate_ld, int n_tokens, int hidden,
                         const void* norm_w, int norm_w_dtype, float eps, void* x_out, void* stream);
 int fx_gather_rows(const void* x, long ldx, const int* rows, void* out, long ldo, int dtype, int n_rows, int width,
                    void* stream);
+// out[r] = w * x[rows[r]], w the routing weight of the (token, rank) pair in place r of the expert order
+int fx_gather_rows_scaled(const void* x, long ldx, const int* rows, const int* inv_perm, const float* weights, int top_k,
+                          void* out, long ldo, int dtype, int n_rows, int width, void* stream);
 int fx_route(const float* logits, long ld, int n_tokens, int n_experts, int top_k, int renorm, int* ids, float* weights,
              int* scratch, int* offsets, int* src_token, int* inv_perm, int* active, int n_slots, void* stream);
 int fx_route_small(const float* logits, long ld, int n_tokens, int n_experts, int top_k, int renorm, int* ids, float* weights,
@@ -86,7 +99,8 @@ int fx_gemm_slab(const void* X, long ldx, const void* W, long ldw, const void* b
 
 int fx_gemm_skinny(const void* X, long ldx, const int* x_rows, const void* W, long ldw, long w_group_stride,
                    const void* bias, int bias_dtype, void* C, int c_dtype, long ldc, int accumulate, int n_tokens,
-                   int N, int K, int gated, int gate_up_offset, const int* group_offsets, const int* active_groups,
+                   int N, int K, int gated, int gate_up_offset, float act_limit, float act_alpha, const int* group_offsets,
+                   const int* active_groups,
                    int n_slots, int tokens_hint, int c_transposed, void* stream);
 int fx_decode_split_mma(const void* q, long ldq, const void* k_pages, const void* v_pages, const int* block_table,
                         int table_width, int page_size, const int* positions, const int* token_seq, const int* seq_slot,
@@ -117,6 +131,22 @@ int fx_decode_attention(const void* q, long ldq, const void* k_pages, const void
                         float* part_ml, int n_tokens, int n_heads, int n_kv_heads, int head_dim, int window,
                         float scale, int split_len, int n_splits, int* status, int* counters, int fresh_positions,
                         int store_new, int write_pages, const float* cos_sin, float softcap, void* stream);
+// attention_prep.cu: what mixers with normed queries and keys, a query temperature, keys and values of different
+// widths, or a latent cache do between their projections and the attention kernel
+int fx_qk_norm_store(void* qkv, int dtype, long ld, const int* positions, const int* token_seq, const int* seq_slot,
+                     const void* wq, const void* wk, int w_dtype, float eps, float temp_coef, int temp_every, void* k_pages,
+                     void* v_pages, const int* block_table, int table_width, int page_size, int n_tokens, int n_heads,
+                     int n_kv_heads, int key_dim, int value_dim, int write_cache, int* status, void* stream);
+int fx_latent_prep(const void* q, long ldq, const void* dkv, long ld_dkv, int dtype, const int* positions,
+                   const int* token_seq, const int* seq_slot, const void* wc, int w_dtype, float eps, const float* cos_sin,
+                   int rot_dims, void* q_plain, void* q_full, void* pages, const int* block_table, int table_width,
+                   int page_size, int n_tokens, int n_heads, int plain_dim, int rot_dim, int rank, int write_cache,
+                   int* status, void* stream);
+int fx_rmsnorm_rows(const void* x, int x_dtype, long ldx, const void* w, int w_dtype, float eps, void* out, int out_dtype,
+                    long ldo, int n_rows, int n, void* stream);
+int fx_heads_to_tokens(const void* in, const void* gate, long ldg, void* out, long ldo, int dtype, int n_tokens,
+                       int n_heads, int width, void* stream);
+
 // softcap c > 0 (fx_paged_attention, fx_prefill_attention, fx_decode_attention): the scaled scores pass through
 // c * tanh(s / c) before the softmax; 0: none.  The kernels that stream pages by TMA take no cap: fx_decode_attention
 // goes to the others, and callers do not give a capped layer to fx_prefill_attention_tc.

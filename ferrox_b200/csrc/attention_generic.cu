@@ -19,23 +19,32 @@
 // reads kv head h / (n_heads / n_kv_heads), scale 1/sqrt(head_dim) :432-449; window
 // = the last W positions, the query's own included :484-524; pages :572-610.
 // CUDA-core arithmetic throughout: this is the 32-bit path and the fallback of the
-// bfloat16 path.  head_dim <= 256.
+// bfloat16 path.
+//
+// Keys and values may differ in width (key_dim <= 640, value_dim <= 512) and in the distance between two
+// positions of a page (ldk, ldv): values that are the leading part of the cached key rows (one latent vector a
+// position, read by every head) are ldv = ldk with v_pages = k_pages.  Queries and outputs are addressed by a
+// token stride and a head stride, so that rows laid out head by head ([head][token][dim]) are read as they lie.
+// `slopes` (optional, one per head): the score of key j for the query at position i is lowered by
+// slopes[h] * (i - j), a bias that grows with the distance.
 #include "common.cuh"
 #include "api.h"
 
 namespace {
 
 constexpr int WARPS = 4;
-constexpr int MAX_D = 256;
+constexpr int MAX_DK = 640;
+constexpr int MAX_DV = 512;
 
-template <typename T>
+template <typename T, int NV>
 __global__ void __launch_bounds__(WARPS * 32) paged_attention_kernel(
-    const T* __restrict__ q, long ldq, const T* __restrict__ k_pages, const T* __restrict__ v_pages,
-    const int* __restrict__ block_table, int table_width, int page_size,
+    const T* __restrict__ q, long ldq, long ldqh, const T* __restrict__ k_pages, const T* __restrict__ v_pages,
+    long ldk, long ldv, const int* __restrict__ block_table, int table_width, int page_size,
     const int* __restrict__ positions, const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
-    T* __restrict__ out, long ldo, int n_heads, int n_kv_heads, int head_dim, int window, float scale, float softcap)
+    T* __restrict__ out, long ldo, long ldoh, int n_heads, int n_kv_heads, int key_dim, int value_dim, int window,
+    float scale, float softcap, const float* __restrict__ slopes)
 {
-    __shared__ float q_s[WARPS][MAX_D];
+    __shared__ float q_s[WARPS][MAX_DK];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x;
     const int h = blockIdx.y * WARPS + warp;
@@ -43,31 +52,32 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_kernel(
     const int kvh = h / (n_heads / n_kv_heads);
     const int pos = positions[t];
     const int* table = block_table + (long)seq_slot[token_seq[t]] * table_width;
-    const T* qh = q + (long)t * ldq + (long)h * head_dim;
-    for (int i = lane; i < head_dim; i += 32) q_s[warp][i] = to_f32(qh[i]) ;
+    const T* qh = q + (long)t * ldq + (long)h * ldqh;
+    for (int i = lane; i < key_dim; i += 32) q_s[warp][i] = to_f32(qh[i]);
     __syncwarp();
+    const float slope = slopes ? slopes[h] : 0.f;
 
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     float m = -INFINITY, l = 0.f;
-    float acc[MAX_D / 32];
+    float acc[NV];
 #pragma unroll
-    for (int i = 0; i < MAX_D / 32; ++i) acc[i] = 0.f;
-    const long head_stride = (long)page_size * head_dim;
+    for (int i = 0; i < NV; ++i) acc[i] = 0.f;
 
     for (int kb = (lo / 32) * 32; kb <= pos; kb += 32) {
         const int key = kb + lane;
         bool valid = key >= lo && key <= pos;
-        long base = -1;
+        long place = -1;      // (page, kv head, position in the page) as one index
         float s = -INFINITY;
         const int page = valid ? table[key / page_size] : -1;
         valid = valid && page >= 0;  // a position without a page is skipped, never dereferenced
         if (valid) {
-            base = ((long)page * n_kv_heads + kvh) * head_stride + (long)(key % page_size) * head_dim;
-            const T* kr = k_pages + base;
+            place = ((long)page * n_kv_heads + kvh) * page_size + (key % page_size);
+            const T* kr = k_pages + place * ldk;
             float dot = 0.f;
-            for (int i = 0; i < head_dim; ++i) dot = fmaf(q_s[warp][i], to_f32(kr[i]), dot);
+            for (int i = 0; i < key_dim; ++i) dot = fmaf(q_s[warp][i], to_f32(kr[i]), dot);
             s = dot * scale;
             if (softcap > 0.f) s = softcap * tanhf(s / softcap);   // soft cap: scores stay inside (-cap, cap)
+            s -= slope * (float)(pos - key);                       // the distance bias
         }
         const float m_new = fmaxf(m, warp_max(s));
         if (m_new == -INFINITY) continue;  // no key of this block is readable (uniform across the warp)
@@ -75,49 +85,83 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_kernel(
         const float alpha = (m == -INFINITY) ? 0.f : expf(m - m_new);
         l = l * alpha + warp_sum(p);
 #pragma unroll
-        for (int i = 0; i < MAX_D / 32; ++i) acc[i] *= alpha;
+        for (int i = 0; i < NV; ++i) acc[i] *= alpha;
         for (int j = 0; j < 32; ++j) {
             const float pj = __shfl_sync(0xffffffffu, p, j);
-            const long bj = __shfl_sync(0xffffffffu, base, j);
+            const long bj = __shfl_sync(0xffffffffu, place, j);
             if (bj < 0) continue;  // uniform across the warp
-            const T* vr = v_pages + bj;
+            const T* vr = v_pages + bj * ldv;
 #pragma unroll
-            for (int i = 0; i < MAX_D / 32; ++i) {
+            for (int i = 0; i < NV; ++i) {
                 const int d = lane + 32 * i;
-                if (d < head_dim) acc[i] = fmaf(pj, to_f32(vr[d]), acc[i]);
+                if (d < value_dim) acc[i] = fmaf(pj, to_f32(vr[d]), acc[i]);
             }
         }
         m = m_new;
     }
     const float inv = l > 0.f ? 1.0f / l : 0.f;
-    T* o = out + (long)t * ldo + (long)h * head_dim;
+    T* o = out + (long)t * ldo + (long)h * ldoh;
 #pragma unroll
-    for (int i = 0; i < MAX_D / 32; ++i) {
+    for (int i = 0; i < NV; ++i) {
         const int d = lane + 32 * i;
-        if (d < head_dim) o[d] = from_f32<T>(acc[i] * inv);
+        if (d < value_dim) o[d] = from_f32<T>(acc[i] * inv);
     }
+}
+
+template <typename T>
+int launch_paged(const void* q, long ldq, long ldqh, const void* k_pages, const void* v_pages, long ldk, long ldv,
+                 const int* block_table, int table_width, int page_size, const int* positions, const int* token_seq,
+                 const int* seq_slot, void* out, long ldo, long ldoh, int n_tokens, int n_heads, int n_kv_heads,
+                 int key_dim, int value_dim, int window, float scale, float softcap, const float* slopes, cudaStream_t s)
+{
+    dim3 grid(n_tokens, (unsigned)fx_cdiv(n_heads, WARPS));
+#define FX_GO(NV)                                                                                                     \
+    paged_attention_kernel<T, NV><<<grid, WARPS * 32, 0, s>>>((const T*)q, ldq, ldqh, (const T*)k_pages,              \
+        (const T*)v_pages, ldk, ldv, block_table, table_width, page_size, positions, token_seq, seq_slot, (T*)out,    \
+        ldo, ldoh, n_heads, n_kv_heads, key_dim, value_dim, window, scale, softcap, slopes)
+    if (value_dim <= 64) FX_GO(2);
+    else if (value_dim <= 128) FX_GO(4);
+    else if (value_dim <= 256) FX_GO(8);
+    else FX_GO(16);
+#undef FX_GO
+    return fx_launch_status();
 }
 
 }  // namespace
 
+// The general form.  Pages: element d of position s of kv head g of page p lies at ((p * n_kv_heads + g) * page_size
+// + s) * ldk + d in k_pages, likewise with ldv in v_pages.
+extern "C" int fx_paged_attention_ex(const void* q, long ldq, long ldqh, const void* k_pages, const void* v_pages,
+                                     long ldk, long ldv, int dtype, const int* block_table, int table_width,
+                                     int page_size, const int* positions, const int* token_seq, const int* seq_slot,
+                                     void* out, long ldo, long ldoh, int n_tokens, int n_heads, int n_kv_heads,
+                                     int key_dim, int value_dim, int window, float scale, float softcap,
+                                     const float* slopes, void* stream)
+{
+    if (n_tokens <= 0) return FX_OK;
+    if (key_dim > MAX_DK || value_dim > MAX_DV || key_dim <= 0 || value_dim <= 0 || n_kv_heads <= 0 ||
+        n_heads % n_kv_heads || ldk < key_dim || ldv < value_dim)
+        return FX_ERR_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == FX_F32)
+        return launch_paged<float>(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, block_table, table_width, page_size,
+                                   positions, token_seq, seq_slot, out, ldo, ldoh, n_tokens, n_heads, n_kv_heads,
+                                   key_dim, value_dim, window, scale, softcap, slopes, s);
+    if (dtype == FX_BF16)
+        return launch_paged<bf16>(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, block_table, table_width, page_size,
+                                  positions, token_seq, seq_slot, out, ldo, ldoh, n_tokens, n_heads, n_kv_heads,
+                                  key_dim, value_dim, window, scale, softcap, slopes, s);
+    return FX_ERR_DTYPE;
+}
+
+// Keys and values of one width, rows of [head][dim] a token.
 extern "C" int fx_paged_attention(const void* q, long ldq, const void* k_pages, const void* v_pages, int dtype,
                                   const int* block_table, int table_width, int page_size, const int* positions,
                                   const int* token_seq, const int* seq_slot, void* out, long ldo, int n_tokens,
                                   int n_heads, int n_kv_heads, int head_dim, int window, float scale, float softcap,
                                   void* stream)
 {
-    if (n_tokens <= 0) return FX_OK;
-    if (head_dim > MAX_D || head_dim <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads) return FX_ERR_SIZE;
-    cudaStream_t s = (cudaStream_t)stream;
-    dim3 grid(n_tokens, (unsigned)fx_cdiv(n_heads, WARPS));
-    if (dtype == FX_F32)
-        paged_attention_kernel<float><<<grid, WARPS * 32, 0, s>>>((const float*)q, ldq, (const float*)k_pages,
-            (const float*)v_pages, block_table, table_width, page_size, positions, token_seq, seq_slot, (float*)out,
-            ldo, n_heads, n_kv_heads, head_dim, window, scale, softcap);
-    else if (dtype == FX_BF16)
-        paged_attention_kernel<bf16><<<grid, WARPS * 32, 0, s>>>((const bf16*)q, ldq, (const bf16*)k_pages,
-            (const bf16*)v_pages, block_table, table_width, page_size, positions, token_seq, seq_slot, (bf16*)out,
-            ldo, n_heads, n_kv_heads, head_dim, window, scale, softcap);
-    else return FX_ERR_DTYPE;
-    return fx_launch_status();
+    return fx_paged_attention_ex(q, ldq, head_dim, k_pages, v_pages, head_dim, head_dim, dtype, block_table, table_width,
+                                 page_size, positions, token_seq, seq_slot, out, ldo, head_dim, n_tokens, n_heads,
+                                 n_kv_heads, head_dim, head_dim, window, scale, softcap, nullptr, stream);
 }

@@ -65,6 +65,16 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floa
     return scratch[32];
 }
 
+// The clamped gated unit of a feed-forward: the gate is capped from above, the up value from both sides, the gate
+// passes through g * sigmoid(alpha g) and multiplies (up + 1).  FAST: the hardware's exponential.
+template <bool FAST>
+__device__ __forceinline__ float fx_clamped_glu(float g, float u, float limit, float alpha) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    const float e = FAST ? __expf(-alpha * g) : expf(-alpha * g);
+    return g / (1.0f + e) * (u + 1.0f);
+}
+
 // Key range [k_begin, k_end) of run `split` of a decoding token at position pos whose first visible key is lo.
 // split_len > 0: runs of split_len keys counted from position 0.  split_len == 0: the token's own visible keys,
 // counted from the multiple of 64 at or below lo, cut into n_splits runs of equal length (a multiple of 64), so

@@ -73,14 +73,16 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
 // silu(x) = x / (1 + exp(-x)) (reference: matmul.rs:268-280).
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, long ld_in, T* __restrict__ out, long ld_out,
-                                const int* __restrict__ n_rows_dev, int rows, int n, int act)
+                                const int* __restrict__ n_rows_dev, int rows, int n, int act, float act_limit,
+                                float act_alpha)
 {
     const long total = (long)(n_rows_dev ? *n_rows_dev : rows) * n;
     for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
         const long r = i / n; const int c = (int)(i - r * n);
         const float g = to_f32(gu[r * ld_in + c]);
         const float u = to_f32(gu[r * ld_in + n + c]);
-        out[r * ld_out + c] = from_f32<T>((act ? fmaxf(g, 0.f) : g / (1.0f + expf(-g))) * u);   // act 1: ReLU
+        out[r * ld_out + c] = from_f32<T>(act == 2 ? fx_clamped_glu<false>(g, u, act_limit, act_alpha)
+                                                   : (act ? fmaxf(g, 0.f) : g / (1.0f + expf(-g))) * u);   // act 1: ReLU
     }
 }
 
@@ -185,7 +187,7 @@ __global__ void moe_combine_kernel(float* __restrict__ h, const T* __restrict__ 
         float acc = 0.f;
         for (int k = 0; k < top_k; ++k) {
             const long r = inv_perm[(long)t * top_k + k];
-            acc = fmaf(topk_w[(long)t * top_k + k], to_f32(y[r * hidden + i]), acc);
+            acc = fmaf(topk_w ? topk_w[(long)t * top_k + k] : 1.f, to_f32(y[r * hidden + i]), acc);
         }
         if (shared) acc = fmaf(g, to_f32(shared[(long)t * hidden + i]), acc);
         h[(long)t * hidden + i] += acc;
@@ -373,7 +375,7 @@ __global__ void moe_combine_vec_kernel(float* __restrict__ h, const T* __restric
         for (int e = 0; e < V; ++e) acc[e] = 0.f;
         for (int k = 0; k < top_k; ++k) {
             const long r = inv_perm[(long)t * top_k + k];
-            const float w = topk_w[(long)t * top_k + k];
+            const float w = topk_w ? topk_w[(long)t * top_k + k] : 1.f;   // no weights: they went into the experts' inputs
             float v[V];
             Pack<T>::load(y + r * hidden + i, v);
 #pragma unroll
@@ -422,7 +424,7 @@ __global__ void moe_combine_norm_kernel(float* __restrict__ h, const T* __restri
         for (int e = 0; e < V; ++e) acc[e] = 0.f;
         for (int k = 0; k < top_k; ++k) {
             const long r = inv_perm[(long)t * top_k + k];
-            const float w = topk_w[(long)t * top_k + k];
+            const float w = topk_w ? topk_w[(long)t * top_k + k] : 1.f;   // no weights: they went into the experts' inputs
             float v[V];
             Pack<T>::load(y + r * hidden + i, v);
 #pragma unroll
@@ -459,6 +461,24 @@ __global__ void moe_combine_norm_kernel(float* __restrict__ h, const T* __restri
 
 inline int threads_for(int n) { int t = 32; while (t < n && t < 1024) t <<= 1; return t; }
 
+// Rows gathered and scaled: out[r] = w * x[rows[r]], w the routing weight of the (token, rank) pair that landed in
+// place r (the rank k with inv_perm[token * top_k + k] == r).  For experts whose weight multiplies their input.
+template <typename T>
+__global__ void gather_rows_scaled_kernel(const T* __restrict__ x, long ldx, const int* __restrict__ rows,
+                                          const int* __restrict__ inv_perm, const float* __restrict__ weights,
+                                          int top_k, T* __restrict__ out, long ldo, int width)
+{
+    fx_pdl_wait();
+    const int r = blockIdx.x;
+    const int t = rows[r];
+    float w = 0.f;
+    for (int k = 0; k < top_k; ++k)
+        if (inv_perm[(long)t * top_k + k] == r) w = weights[(long)t * top_k + k];
+    const T* src = x + (long)t * ldx;
+    T* dst = out + (long)r * ldo;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = from_f32<T>(w * to_f32(src[i]));
+}
+
 }  // namespace
 
 extern "C" int fx_embed(const void* table, int dtype, const int* ids, float* out, int n_tokens, int hidden,
@@ -494,24 +514,24 @@ extern "C" int fx_rmsnorm(const float* x, const int* rows, const void* w, int w_
 }
 
 extern "C" int fx_glu_mul(const void* gu, long ld_in, void* out, long ld_out, int dtype, const int* n_rows_dev,
-                          int rows, int n, int act, void* stream);
+                          int rows, int n, int act, float act_limit, float act_alpha, void* stream);
 
 extern "C" int fx_silu_mul(const void* gu, long ld_in, void* out, long ld_out, int dtype, const int* n_rows_dev,
                            int rows, int n, void* stream)
 {
-    return fx_glu_mul(gu, ld_in, out, ld_out, dtype, n_rows_dev, rows, n, 0, stream);
+    return fx_glu_mul(gu, ld_in, out, ld_out, dtype, n_rows_dev, rows, n, 0, 0.f, 0.f, stream);
 }
 
-// act(gate) * up over rows of [gate | up]; act 0: SiLU, 1: ReLU.
+// act(gate) * up over rows of [gate | up]; act 0: SiLU, 1: ReLU; 2: the clamped unit (fx_clamped_glu).
 extern "C" int fx_glu_mul(const void* gu, long ld_in, void* out, long ld_out, int dtype, const int* n_rows_dev,
-                          int rows, int n, int act, void* stream)
+                          int rows, int n, int act, float act_limit, float act_alpha, void* stream)
 {
     if (rows <= 0 || n <= 0) return FX_OK;
     cudaStream_t s = (cudaStream_t)stream;
     long blocks = fx_cdiv((long)rows * n, 256);
     if (blocks > fx_sm_count() * 16L) blocks = fx_sm_count() * 16L;
-    if (dtype == FX_F32) silu_mul_kernel<float><<<(unsigned)blocks, 256, 0, s>>>((const float*)gu, ld_in, (float*)out, ld_out, n_rows_dev, rows, n, act);
-    else if (dtype == FX_BF16) silu_mul_kernel<bf16><<<(unsigned)blocks, 256, 0, s>>>((const bf16*)gu, ld_in, (bf16*)out, ld_out, n_rows_dev, rows, n, act);
+    if (dtype == FX_F32) silu_mul_kernel<float><<<(unsigned)blocks, 256, 0, s>>>((const float*)gu, ld_in, (float*)out, ld_out, n_rows_dev, rows, n, act, act_limit, act_alpha);
+    else if (dtype == FX_BF16) silu_mul_kernel<bf16><<<(unsigned)blocks, 256, 0, s>>>((const bf16*)gu, ld_in, (bf16*)out, ld_out, n_rows_dev, rows, n, act, act_limit, act_alpha);
     else return FX_ERR_DTYPE;
     return fx_launch_status();
 }
@@ -620,6 +640,22 @@ extern "C" int fx_moe_combine_norm(float* h, const void* y, int dtype, const int
     if (dtype == FX_F32) { if (ch <= 1) FX_GO(float, 1); else if (ch == 2) FX_GO(float, 2); else FX_GO(float, 4); }
     else { if (ch <= 1) FX_GO(bf16, 1); else if (ch == 2) FX_GO(bf16, 2); else FX_GO(bf16, 4); }
 #undef FX_GO
+    return fx_launch_status();
+}
+
+
+extern "C" int fx_gather_rows_scaled(const void* x, long ldx, const int* rows, const int* inv_perm, const float* weights,
+                                     int top_k, void* out, long ldo, int dtype, int n_rows, int width, void* stream)
+{
+    if (n_rows <= 0 || width <= 0) return FX_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == FX_F32)
+        fx_launch_pdl(gather_rows_scaled_kernel<float>, n_rows, 128, 0, s, (const float*)x, ldx, rows, inv_perm, weights, top_k,
+                      (float*)out, ldo, width);
+    else if (dtype == FX_BF16)
+        fx_launch_pdl(gather_rows_scaled_kernel<bf16>, n_rows, 128, 0, s, (const bf16*)x, ldx, rows, inv_perm, weights, top_k,
+                      (bf16*)out, ldo, width);
+    else return FX_ERR_DTYPE;
     return fx_launch_status();
 }
 

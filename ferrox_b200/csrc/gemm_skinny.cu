@@ -50,7 +50,8 @@ struct SkinnyArgs {
     int c_transposed;              // store C[n][r] instead of C[r][n] (ldc is then the pitch of a feature's row)
     int n_tokens; int N; int K;
     int gate_up_offset;            // gated form: row of `up` matching gate row i is i + gate_up_offset
-    int act;                       // gated form: 0 SiLU, 1 ReLU on the gate
+    int act;                       // gated form: 0 SiLU, 1 ReLU on the gate, 2 the clamped unit (fx_clamped_glu)
+    float act_limit, act_alpha;
     const int* group_offsets;      // grouped form: rows [off[e], off[e+1]) belong to expert e
     const int* active_groups;      // grouped form: the experts that got rows, then -1
     int n_slots;                   // length of active_groups
@@ -200,7 +201,8 @@ __global__ void __launch_bounds__(NTHREADS) skinny_kernel(SkinnyArgs a)
                     if (GATED) up += red[w][1][j][f][tn];
                 }
                 if (a.bias) v += load_any(a.bias, a.bias_dtype, n);
-                if (MODE == 1) v = (a.act ? fmaxf(v, 0.f) : v / (1.0f + expf(-v))) * up;
+                if (MODE == 1) v = a.act == 2 ? fx_clamped_glu<false>(v, up, a.act_limit, a.act_alpha)
+                                               : (a.act ? fmaxf(v, 0.f) : v / (1.0f + expf(-v))) * up;
                 auto store = [&](int col, float val) {
                     const long at = a.c_transposed ? (long)col * a.ldc + r : (long)r * a.ldc + col;
                     if (a.c_dtype == FX_F32) {
@@ -239,7 +241,7 @@ int launch_nt(const SkinnyArgs& a, int max_tokens_per_group, dim3 grid, cudaStre
 // Refuses (FX_ERR_SIZE / FX_ERR_ALIGN) K not a multiple of 32 and rows not 16-byte aligned.
 extern "C" int fx_gemm_skinny(const void* X, long ldx, const int* x_rows, const void* W, long ldw, long w_group_stride,
                               const void* bias, int bias_dtype, void* C, int c_dtype, long ldc, int accumulate,
-                              int n_tokens, int N, int K, int gated, int gate_up_offset,
+                              int n_tokens, int N, int K, int gated, int gate_up_offset, float act_limit, float act_alpha,
                               const int* group_offsets, const int* active_groups, int n_slots, int tokens_hint,
                               int c_transposed, void* stream)
 {
@@ -252,7 +254,7 @@ extern "C" int fx_gemm_skinny(const void* X, long ldx, const int* x_rows, const 
     a.X = (const bf16*)X; a.ldx = ldx; a.x_rows = x_rows;
     a.bias = bias; a.bias_dtype = bias_dtype;
     a.C = C; a.ldc = ldc; a.c_dtype = c_dtype; a.accumulate = accumulate; a.c_transposed = c_transposed;
-    a.n_tokens = n_tokens; a.N = N; a.K = K; a.gate_up_offset = gate_up_offset; a.act = gated == 2;
+    a.n_tokens = n_tokens; a.N = N; a.K = K; a.gate_up_offset = gate_up_offset; a.act = gated > 0 ? gated - 1 : 0; a.act_limit = act_limit; a.act_alpha = act_alpha;
     a.group_offsets = group_offsets; a.active_groups = active_groups; a.n_slots = n_slots;
     // grouped: one block row per expert slot (many short blocks hide each other's start-up better than
     // few long ones; measured)

@@ -51,7 +51,9 @@ struct TcArgs {
     const void* bias; int bias_dtype;
     int M, N, K;
     int gate_up_offset;             // gated: W row of `up` feature j is gate_up_offset + j
-    int act;                        // gated: what the gate passes through before it multiplies `up`: 0 SiLU, 1 ReLU
+    int act;                        // gated: what the gate passes through before it multiplies `up`: 0 SiLU, 1 ReLU,
+                                    // 2 the clamped unit (fx_clamped_glu) with act_limit and act_alpha
+    float act_limit, act_alpha;
     const int* group_offsets;       // grouped: rows [off[e], off[e+1]) use matrix e
     int n_groups;
     int* status;
@@ -274,7 +276,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const __grid_const
                 for (int j = 0; j < 32; ++j) {
                     float x = __uint_as_float(r[j]);
                     if (a.bias) x += bias_s[quad][c * 32 + j];
-                    if (GATED) x = (a.act ? fmaxf(x, 0.f) : __fdividef(x, 1.0f + __expf(-x))) * __uint_as_float(u[j]);
+                    if (GATED) x = a.act == 2 ? fx_clamped_glu<true>(x, __uint_as_float(u[j]), a.act_limit, a.act_alpha)
+                                           : (a.act ? fmaxf(x, 0.f) : __fdividef(x, 1.0f + __expf(-x))) * __uint_as_float(u[j]);
                     v[j] = x;
                 }
                 if (fast) {
@@ -401,7 +404,8 @@ int run_bn(const void* X, long ldx, const void* W, long ldw, long w_group_stride
 // rows of X (and of C) sorted by group; M is then the total number of rows.
 extern "C" int fx_gemm_tc(const void* X, long ldx, const void* W, long ldw, long w_group_stride, int w_rows,
                           const void* bias, int bias_dtype, void* C, int c_dtype, long ldc, int accumulate,
-                          int M, int N, int K, int gated, int gate_up_offset, const int* group_offsets, int n_groups,
+                          int M, int N, int K, int gated, int gate_up_offset, float act_limit, float act_alpha,
+                          const int* group_offsets, int n_groups,
                           int* status, void* stream)
 {
     if (M <= 0 || N <= 0) return FX_OK;
@@ -412,7 +416,7 @@ extern "C" int fx_gemm_tc(const void* X, long ldx, const void* W, long ldw, long
     TcArgs a;
     a.C = C; a.ldc = ldc; a.c_dtype = c_dtype; a.accumulate = accumulate;
     a.bias = bias; a.bias_dtype = bias_dtype;
-    a.M = M; a.N = N; a.K = K; a.gate_up_offset = gate_up_offset; a.act = gated == 2;
+    a.M = M; a.N = N; a.K = K; a.gate_up_offset = gate_up_offset; a.act = gated > 0 ? gated - 1 : 0; a.act_limit = act_limit; a.act_alpha = act_alpha;
     a.group_offsets = group_offsets; a.n_groups = n_groups; a.status = status;
     cudaStream_t s = (cudaStream_t)stream;
     // wide outputs take 128 x 256 tiles (fewer bytes fetched per flop; measured faster even when they give

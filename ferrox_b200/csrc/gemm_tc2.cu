@@ -41,7 +41,8 @@ struct Tc2Args {
     const void* bias; int bias_dtype;
     int M, N, K;
     int gate_up_offset;
-    int act;                        // gated: 0 SiLU, 1 ReLU on the gate
+    int act;                        // gated: 0 SiLU, 1 ReLU on the gate, 2 the clamped unit (fx_clamped_glu)
+    float act_limit, act_alpha;
     int gated;
     int* status;
 };
@@ -240,7 +241,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc2_kernel(const __grid_cons
                 for (int j = 0; j < 32; ++j) {
                     float x = __uint_as_float(r[j]);
                     if (a.bias) x += bias_s[quad][c * 32 + j];
-                    if (GATED) x = (a.act ? fmaxf(x, 0.f) : __fdividef(x, 1.0f + __expf(-x))) * __uint_as_float(u[j]);
+                    if (GATED) x = a.act == 2 ? fx_clamped_glu<true>(x, __uint_as_float(u[j]), a.act_limit, a.act_alpha)
+                                           : (a.act ? fmaxf(x, 0.f) : __fdividef(x, 1.0f + __expf(-x))) * __uint_as_float(u[j]);
                     v[j] = x;
                 }
                 if (fast) {
@@ -331,7 +333,7 @@ bool make_map(CUtensorMap* map, const void* ptr, uint64_t K, uint64_t rows, uint
 // [gate_up_offset, gate_up_offset + N), C = act(gate) * up (gated 1: SiLU, 2: ReLU).  Dense products only (no groups).
 extern "C" int fx_gemm_tc2(const void* X, long ldx, const void* W, long ldw, int w_rows, const void* bias, int bias_dtype,
                            void* C, int c_dtype, long ldc, int accumulate, int M, int N, int K, int gated,
-                           int gate_up_offset, int* status, void* stream)
+                           int gate_up_offset, float act_limit, float act_alpha, int* status, void* stream)
 {
     if (M <= 0 || N <= 0) return FX_OK;
     if (K <= 0 || K % 8) return FX_ERR_SIZE;
@@ -340,7 +342,7 @@ extern "C" int fx_gemm_tc2(const void* X, long ldx, const void* W, long ldw, int
     Tc2Args a;
     a.C = C; a.ldc = ldc; a.c_dtype = c_dtype; a.accumulate = accumulate;
     a.bias = bias; a.bias_dtype = bias_dtype;
-    a.M = M; a.N = N; a.K = K; a.gate_up_offset = gate_up_offset; a.gated = gated; a.act = gated == 2; a.status = status;
+    a.M = M; a.N = N; a.K = K; a.gate_up_offset = gate_up_offset; a.gated = gated; a.act = gated > 0 ? gated - 1 : 0; a.act_limit = act_limit; a.act_alpha = act_alpha; a.status = status;
     CUtensorMap ma, mb;
     if (!make_map(&ma, X, (uint64_t)K, (uint64_t)M, (uint64_t)ldx, BM)) return FX_ERR_SIZE;
     if (!make_map(&mb, W, (uint64_t)K, (uint64_t)w_rows, (uint64_t)ldw, BNH)) return FX_ERR_SIZE;

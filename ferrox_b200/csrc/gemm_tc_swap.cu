@@ -54,7 +54,8 @@ struct SwArgs {
     const void* bias; int bias_dtype;
     int M, N, K;
     int gate_up_offset;
-    int act;                        // gated: 0 SiLU, 1 ReLU on the gate
+    int act;                        // gated: 0 SiLU, 1 ReLU on the gate, 2 the clamped unit (fx_clamped_glu)
+    float act_limit, act_alpha;
     const int* group_offsets;
     int n_groups;
     int weights_first;
@@ -275,7 +276,8 @@ __global__ void __launch_bounds__(NTHREADS, (TNB <= 32 ? 2 : 1)) gemm_tc_swap_ke
                 for (int j = 0; j < 32; ++j) {
                     if (row0 + j >= t.row_end) break;
                     float x = __uint_as_float(r[j]) + bias;
-                    if (GATED) x = (a.act ? fmaxf(x, 0.f) : x / (1.0f + __expf(-x))) * __uint_as_float(u[j]);
+                    if (GATED) x = a.act == 2 ? fx_clamped_glu<true>(x, __uint_as_float(u[j]), a.act_limit, a.act_alpha)
+                                           : (a.act ? fmaxf(x, 0.f) : x / (1.0f + __expf(-x))) * __uint_as_float(u[j]);
                     if (a.k_splits > 1) {   // a run of K: the plain partial sum
                         a.partials[((long)t.split * a.M + row0 + j) * a.N + f] = __uint_as_float(r[j]);
                         continue;
@@ -387,7 +389,8 @@ int run_tnb(const void* X, long ldx, const void* W, long ldw, long w_group_strid
 // products do not overlap.
 extern "C" int fx_gemm_tc_swap(const void* X, long ldx, const void* W, long ldw, long w_group_stride, int w_rows,
                                const void* bias, int bias_dtype, void* C, int c_dtype, long ldc, int accumulate,
-                               int M, int N, int K, int gated, int gate_up_offset, const int* group_offsets, int n_groups,
+                               int M, int N, int K, int gated, int gate_up_offset, float act_limit, float act_alpha,
+                               const int* group_offsets, int n_groups,
                                int tokens_per_tile, int weights_first, int k_splits, float* partials, int* status,
                                void* stream)
 {
@@ -399,7 +402,7 @@ extern "C" int fx_gemm_tc_swap(const void* X, long ldx, const void* W, long ldw,
     SwArgs a;
     a.C = C; a.ldc = ldc; a.c_dtype = c_dtype; a.accumulate = accumulate;
     a.bias = bias; a.bias_dtype = bias_dtype;
-    a.M = M; a.N = N; a.K = K; a.gate_up_offset = gate_up_offset; a.act = gated == 2;
+    a.M = M; a.N = N; a.K = K; a.gate_up_offset = gate_up_offset; a.act = gated > 0 ? gated - 1 : 0; a.act_limit = act_limit; a.act_alpha = act_alpha;
     a.group_offsets = group_offsets; a.n_groups = n_groups; a.status = status; a.weights_first = weights_first;
     a.k_splits = k_splits > 1 ? k_splits : 1; a.partials = partials;
     if (a.k_splits > 1 && (group_offsets || gated || !partials || a.k_splits > (K + BK - 1) / BK)) return FX_ERR_SIZE;

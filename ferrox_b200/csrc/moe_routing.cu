@@ -8,7 +8,8 @@ namespace {
 
 // One warp per token.  p = softmax(logits) over ALL experts (max-subtracted), the k
 // largest p are kept in descending order, on equal p the lowest expert index wins,
-// and the weights are the kept p, divided by their sum when `renorm` is set
+// and the weights are the kept p, divided by their sum when bit 0 of `renorm` is set.  Bit 1 of `renorm`: the
+// weights are sigmoid(logit) of the kept experts instead (the same experts: both scores rise with the logit).
 // (reference: crates/ferrox-moe/src/lib.rs:333-355; lowest-index tie-break as in
 // its GPU kernel, crates/ferrox-metal/src/gpu.rs:686-699).
 // In shared memory a probability is kept as its bit pattern plus one (probabilities are >= 0, so the patterns
@@ -38,7 +39,7 @@ __device__ __forceinline__ void route_token(const float* __restrict__ lg, float*
         }
         const uint32_t top = __reduce_max_sync(0xffffffffu, best);
         const int win = __reduce_min_sync(0xffffffffu, best == top ? best_e : 0x7fffffff);
-        const float w = __uint_as_float(top - 1u) / sum;
+        const float w = (renorm & 2) ? 1.0f / (1.0f + expf(-lg[win])) : __uint_as_float(top - 1u) / sum;
         if (lane == 0) {
             pb[win] = 0u;
             if (!in_regs) {
@@ -54,11 +55,11 @@ __device__ __forceinline__ void route_token(const float* __restrict__ lg, float*
     if (in_regs) {
         if (lane < top_k) {
             ids[(long)t * top_k + lane] = mine_e;
-            weights[(long)t * top_k + lane] = renorm ? mine_w / kept : mine_w;
+            weights[(long)t * top_k + lane] = (renorm & 1) ? mine_w / kept : mine_w;
             if (ids_shared) ids_shared[t * top_k + lane] = mine_e;
             if (counts) atomicAdd(&counts[mine_e], 1);
         }
-    } else if (renorm) {
+    } else if (renorm & 1) {
         __syncwarp();
         for (int k = lane; k < top_k; k += 32) weights[(long)t * top_k + k] /= kept;
     }

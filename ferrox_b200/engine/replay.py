@@ -44,7 +44,7 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most positions live requests hold at any time (each rounded up to a page)")
     ap.add_argument("--page-size", type=int, default=64, help="positions per cache page (default 64)")
-    ap.add_argument("--max-requests", type=int, default=8, help="most requests live at a time")
+    ap.add_argument("--max-requests", type=int, default=4, help="most requests live at a time (default 4)")
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
 

@@ -41,10 +41,19 @@ _SIGNATURES = {
     "fx_silu_mul": [_P, _L, _P, _L, _I, _P, _I, _I, _P],
     "fx_rope_kv_write": [_P, _I, _L, _P, _P, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "fx_rope_table": [_P, _P, _I, _I, _P, _P],
-    "fx_gemm_tc": [_P, _L, _P, _L, _L, _I, _P, _I, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _I, _P, _P],
-    "fx_gemm_tc_swap": [_P, _L, _P, _L, _L, _I, _P, _I, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _I, _I, _I, _I, _P, _P, _P],
-    "fx_gemm_tc2": [_P, _L, _P, _L, _I, _P, _I, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _P],
+    "fx_gemm_tc": [_P, _L, _P, _L, _L, _I, _P, _I, _P, _I, _L, _I, _I, _I, _I, _I, _I, _F, _F, _P, _I, _P, _P],
+    "fx_gemm_tc_swap": [_P, _L, _P, _L, _L, _I, _P, _I, _P, _I, _L, _I, _I, _I, _I, _I, _I, _F, _F, _P, _I, _I, _I, _I, _P, _P,
+                        _P],
+    "fx_gemm_tc2": [_P, _L, _P, _L, _I, _P, _I, _P, _I, _L, _I, _I, _I, _I, _I, _I, _F, _F, _P, _P],
     "fx_gather_rows": [_P, _L, _P, _P, _L, _I, _I, _I, _P],
+    "fx_gather_rows_scaled": [_P, _L, _P, _P, _P, _I, _P, _L, _I, _I, _I, _P],
+    "fx_paged_attention_ex": [_P, _L, _L, _P, _P, _L, _L, _I, _P, _I, _I, _P, _P, _P, _P, _L, _L, _I, _I, _I, _I, _I, _I, _F,
+                              _F, _P, _P],
+    "fx_qk_norm_store": [_P, _I, _L, _P, _P, _P, _P, _P, _I, _F, _F, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "fx_latent_prep": [_P, _L, _P, _L, _I, _P, _P, _P, _P, _I, _F, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P,
+                       _P],
+    "fx_rmsnorm_rows": [_P, _I, _L, _P, _I, _F, _P, _I, _L, _I, _I, _P],
+    "fx_heads_to_tokens": [_P, _P, _L, _P, _L, _I, _I, _I, _I, _P],
     "fx_route_small": [_P, _L, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P],
     "fx_route": [_P, _L, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _P],
     "fx_route_fused": [_P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _P, _L, _P, _P, _P, _P, _P, _P, _I, _P, _L, _P],
@@ -52,7 +61,7 @@ _SIGNATURES = {
     "fx_moe_combine_norm": [_P, _P, _I, _P, _P, _I, _P, _P, _L, _I, _I, _P, _I, _F, _P, _P],
     "fx_residual_add": [_P, _P, _I, _L, _P],
     "fx_paged_attention": [_P, _L, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _F, _F, _P],
-    "fx_glu_mul": [_P, _L, _P, _L, _I, _P, _I, _I, _I, _P],
+    "fx_glu_mul": [_P, _L, _P, _L, _I, _P, _I, _I, _I, _F, _F, _P],
     "fx_layernorm": [_P, _P, _P, _I, _F, _P, _I, _I, _I, _P],
     "fx_layernorm_residual": [_P, _P, _I, _F, _P, _I, _F, _P, _I, _F, _P, _I, _F, _P, _I, _I, _I, _P],
     "fx_scale": [_P, _L, _F, _P],
@@ -67,7 +76,7 @@ _SIGNATURES = {
     "fx_moe_align": [_P, _I, _I, _I, _P, _P, _P, _P, _P, _I, _P],
     "fx_gemm_slab_ok": [_I, _I, _I],
     "fx_gemm_slab": [_P, _L, _P, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _P, _P],
-    "fx_gemm_skinny": [_P, _L, _P, _P, _L, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _P, _I, _I, _I, _P],
+    "fx_gemm_skinny": [_P, _L, _P, _P, _L, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _I, _I, _F, _F, _P, _P, _I, _I, _I, _P],
     "fx_decode_attention": [_P, _L, _P, _P, _I, _I, _P, _I, _I, _P, _P, _P, _P, _L, _P, _P, _I, _I, _I, _I, _I, _F, _I,
                             _I, _P, _P, _I, _I, _I, _P, _F, _P],
     "fx_argmax": [_P, _L, _I, _I, _P, _P],
@@ -285,14 +294,34 @@ def rmsnorm(x, weight, eps, out, rows=None, stream=None):
     return out
 
 
-GATE_ACTIVATIONS = {"silu": 0, "relu": 1}   # what a gated feed-forward passes its gate through
+GATE_ACTIVATIONS = {"silu": 0, "relu": 1, "clamped_swish": 2}   # what a gated feed-forward passes its gate through
 
 
-def gate_code(activation: str) -> int:
+def gate_code(activation) -> int:
+    """``activation``: a name, or (name, limit, alpha) for the clamped unit
+    min(g, limit) * sigmoid(alpha * min(g, limit)) * (clamp(u, -limit, limit) + 1)."""
+    name = activation[0] if isinstance(activation, tuple) else activation
     try:
-        return GATE_ACTIVATIONS[activation]
-    except KeyError:
+        c = GATE_ACTIVATIONS[name]
+    except (KeyError, TypeError):
         raise KernelError(f"gate activation {activation!r}: the kernels know {', '.join(GATE_ACTIVATIONS)}") from None
+    if (c == 2) != isinstance(activation, tuple) or (c == 2 and len(activation) != 3):
+        raise KernelError("the clamped gate activation is given as (name, limit, alpha), the others by name")
+    return c
+
+
+def _gate_args(gated):
+    """The kernels' (gated, act_limit, act_alpha): ``gated`` is 0 / False (plain), 1 / True (SiLU gate), 2 (ReLU gate)
+    or (3, limit, alpha) (the clamped unit)."""
+    if isinstance(gated, tuple):
+        return int(gated[0]), float(gated[1]), float(gated[2])
+    return int(gated), 0.0, 0.0
+
+
+def gated_arg(activation):
+    """What the product kernels take as ``gated`` for a gate activation (see :func:`gate_code`)."""
+    c = gate_code(activation)
+    return (3, float(activation[1]), float(activation[2])) if c == 2 else 1 + c
 
 
 def silu_mul(gu, out, stream=None, activation="silu"):
@@ -300,8 +329,9 @@ def silu_mul(gu, out, stream=None, activation="silu"):
     rows, n = out.shape
     if gu.shape[1] != 2 * n:
         raise KernelError("silu_mul expects [gate | up] rows of twice the output width")
+    lim, alpha = (float(activation[1]), float(activation[2])) if isinstance(activation, tuple) else (0.0, 0.0)
     call("fx_glu_mul", _ptr(gu), _rows(gu), _ptr(out), _rows(out), code(gu), None, rows, n, gate_code(activation),
-         stream if stream is not None else stream_ptr())
+         lim, alpha, stream if stream is not None else stream_ptr())
     return out
 
 
@@ -448,6 +478,7 @@ def route(logits, top_k, renorm, ids, weights, scratch, offsets, src_token, inv_
 
 
 PAIR_HALVES, PAIR_ADJACENT = 0, 1
+ATTENTION_MAX_KEY_DIM, ATTENTION_MAX_VALUE_DIM = 640, 512    # what the general attention kernels hold of a row
 
 
 def rope_kv_write(qkv, positions, token_seq, seq_slot, inv_freq, rotary_dim, k_pages, v_pages, block_table, page_size,
@@ -472,6 +503,71 @@ def paged_attention(q, k_pages, v_pages, block_table, page_size, positions, toke
          block_table.shape[1], page_size, _ptr(positions), _ptr(token_seq), _ptr(seq_slot), _ptr(out), _rows(out), T,
          n_heads, n_kv_heads, head_dim, int(window or 0), float(scale), float(softcap or 0.0),
          stream if stream is not None else stream_ptr())
+    return out
+
+
+def paged_attention_ex(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, block_table, page_size, positions, token_seq, seq_slot,
+                       out, ldo, ldoh, n_heads, n_kv_heads, key_dim, value_dim, window, scale, softcap=None, slopes=None,
+                       stream=None):
+    """:func:`paged_attention` in its general form: keys of ``key_dim`` and values of ``value_dim`` elements whose
+    positions lie ``ldk`` / ``ldv`` elements apart in their pages (values that are the leading part of the cached
+    key rows: the same tensor twice with ldv = ldk); ``q`` and ``out`` are any tensors addressed by a token stride
+    and a head stride; ``slopes`` (float32 [n_heads], optional): slopes[h] * (i - j) is taken off the score of key j
+    for the query at position i."""
+    T = positions.numel()
+    if slopes is not None and (slopes.dtype != torch.float32 or slopes.numel() != n_heads):
+        raise KernelError("paged_attention_ex: one 32-bit slope per head")
+    call("fx_paged_attention_ex", _ptr(q), int(ldq), int(ldqh), _ptr(k_pages), _ptr(v_pages), int(ldk), int(ldv), code(q),
+         _ptr(block_table), block_table.shape[1], page_size, _ptr(positions), _ptr(token_seq), _ptr(seq_slot), _ptr(out),
+         int(ldo), int(ldoh), T, n_heads, n_kv_heads, key_dim, value_dim, int(window or 0), float(scale),
+         float(softcap or 0.0), _ptr(slopes), stream if stream is not None else stream_ptr())
+    return out
+
+
+def qk_norm_store(qkv, positions, token_seq, seq_slot, q_weight, k_weight, eps, temperature, k_pages, v_pages, block_table,
+                  page_size, n_heads, n_kv_heads, key_dim, value_dim, write_cache=True, status=None, stream=None):
+    """Rows of [q heads | k heads | v heads] (widths key_dim, key_dim, value_dim), in place: q and k normed per head
+    (x / sqrt(mean(x^2) + eps) * weight; weights [key_dim] or None), q times the query temperature
+    1 + coef * ln(floor((pos + 1) / every) + 1) (``temperature`` = (coef, every) or None); k and v stored in their
+    pages ([pages, kv heads, page, key_dim] and [.., value_dim])."""
+    coef, every = temperature if temperature is not None else (0.0, 0)
+    if (q_weight is None) != (k_weight is None):
+        raise KernelError("qk_norm_store: both norm weights or none")
+    call("fx_qk_norm_store", _ptr(qkv), code(qkv), _rows(qkv), _ptr(positions), _ptr(token_seq), _ptr(seq_slot),
+         _ptr(q_weight), _ptr(k_weight), code(q_weight) if q_weight is not None else 0, float(eps), float(coef), int(every),
+         _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1], page_size, qkv.shape[0], n_heads,
+         n_kv_heads, key_dim, value_dim, int(write_cache), _ptr(status), stream if stream is not None else stream_ptr())
+
+
+def latent_prep(q, dkv, positions, token_seq, seq_slot, c_weight, eps, cos_sin, rot_dims, q_plain, q_full, pages,
+                block_table, page_size, n_heads, plain_dim, rot_dim, rank, write_cache=True, status=None, stream=None):
+    """The step between a latent attention's projections and its attention kernel: ``dkv`` rows [rank | rot_dim] become
+    the cached row (the latent normed with ``c_weight``, the key part rotated on neighbouring pairs by ``cos_sin``
+    [T, rot_dims / 2, 2]); ``q`` rows of heads [plain_dim | rot_dim] are split into ``q_plain`` [heads, T, plain_dim]
+    and the rotated part in columns rank.. of ``q_full`` [heads, T, rank + rot_dim]."""
+    T = q.shape[0]
+    call("fx_latent_prep", _ptr(q), _rows(q), _ptr(dkv), _rows(dkv), code(q), _ptr(positions), _ptr(token_seq),
+         _ptr(seq_slot), _ptr(c_weight), code(c_weight), float(eps), _ptr(cos_sin), int(rot_dims), _ptr(q_plain),
+         _ptr(q_full), _ptr(pages), _ptr(block_table), block_table.shape[1], page_size, T, n_heads, plain_dim, rot_dim,
+         rank, int(write_cache), _ptr(status), stream if stream is not None else stream_ptr())
+
+
+def rmsnorm_rows(x, weight, eps, out, stream=None):
+    """out = x / sqrt(mean(x^2) + eps) * weight over the rows of any 2-D views with contiguous rows (either
+    element type on either side; 32-bit arithmetic)."""
+    call("fx_rmsnorm_rows", _ptr(x), code(x), _rows(x), _ptr(weight), code(weight), float(eps), _ptr(out), code(out),
+         _rows(out), x.shape[0], x.shape[1], stream if stream is not None else stream_ptr())
+    return out
+
+
+def heads_to_tokens(x, out, gate=None, stream=None):
+    """out[t, h * V + v] = x[h, t, v] (* sigmoid(gate[t, h * V + v])): rows laid out head by head back into token
+    rows.  ``x`` contiguous [heads, T, V]; ``gate`` a row view of out's width."""
+    H, T, V = x.shape
+    if not x.is_contiguous() or (gate is not None and gate.dtype != x.dtype) or out.dtype != x.dtype:
+        raise KernelError("heads_to_tokens: contiguous [heads, tokens, width] and one element type")
+    call("fx_heads_to_tokens", _ptr(x), _ptr(gate), _rows(gate) if gate is not None else 0, _ptr(out), _rows(out), code(x),
+         T, H, V, stream if stream is not None else stream_ptr())
     return out
 
 
@@ -639,11 +735,12 @@ def gemm_skinny(x, w, out, *, bias=None, accumulate=False, gated=False, x_rows=N
     else:
         wrows, wstride, ldw = w.shape[0], 0, w.stride(0)
         n_slots = 1
+    gated, lim, alpha = _gate_args(gated)
     if wrows != (2 * N if gated else N) or w.shape[-1] != K:
         raise KernelError(f"gemm_skinny shapes do not agree: x {tuple(x.shape)} w {tuple(w.shape)} out {tuple(out.shape)}")
     call("fx_gemm_skinny", _ptr(x), _rows(x), _ptr(x_rows), _ptr(w), ldw, wstride, _ptr(bias),
          code(bias) if bias is not None else 0, _ptr(out), code(out), _rows(out), int(accumulate), rows, N, K,
-         int(gated), N if gated else 0, _ptr(group_offsets), _ptr(active_groups), n_slots, int(tokens_hint),
+         int(gated), N if gated else 0, lim, alpha, _ptr(group_offsets), _ptr(active_groups), n_slots, int(tokens_hint),
          int(transposed_out), stream if stream is not None else stream_ptr())
     return out
 
@@ -790,10 +887,11 @@ def gemm_tc(x, w, out, *, bias=None, accumulate=False, gated=False, group_offset
         G, wrows, ldw, wstride = w.shape[0], w.shape[1], w.stride(1), w.stride(0)
     else:
         G, wrows, ldw, wstride = 0, w.shape[0], w.stride(0), 0
+    gated, lim, alpha = _gate_args(gated)
     if wrows != (2 * N if gated else N) or w.shape[-1] != K or x.shape[0] != M:
         raise KernelError(f"gemm_tc shapes do not agree: x {tuple(x.shape)} w {tuple(w.shape)} out {tuple(out.shape)}")
     call("fx_gemm_tc", _ptr(x), _rows(x), _ptr(w), ldw, wstride, wrows, _ptr(bias), code(bias) if bias is not None else 0,
-         _ptr(out), code(out), _rows(out), int(accumulate), M, N, K, int(gated), N if gated else 0,
+         _ptr(out), code(out), _rows(out), int(accumulate), M, N, K, int(gated), N if gated else 0, lim, alpha,
          _ptr(group_offsets), G, _ptr(status), stream if stream is not None else stream_ptr())
     return out
 
@@ -813,10 +911,11 @@ def gemm_tc_swap(x, w, out, *, bias=None, accumulate=False, gated=False, group_o
         G, wrows, ldw, wstride = w.shape[0], w.shape[1], w.stride(1), w.stride(0)
     else:
         G, wrows, ldw, wstride = 0, w.shape[0], w.stride(0), 0
+    gated, lim, alpha = _gate_args(gated)
     if wrows != (2 * N if gated else N) or w.shape[-1] != K or x.shape[0] != M:
         raise KernelError(f"gemm_tc_swap shapes do not agree: x {tuple(x.shape)} w {tuple(w.shape)} out {tuple(out.shape)}")
     call("fx_gemm_tc_swap", _ptr(x), _rows(x), _ptr(w), ldw, wstride, wrows, _ptr(bias), code(bias) if bias is not None else 0,
-         _ptr(out), code(out), _rows(out), int(accumulate), M, N, K, int(gated), N if gated else 0,
+         _ptr(out), code(out), _rows(out), int(accumulate), M, N, K, int(gated), N if gated else 0, lim, alpha,
          _ptr(group_offsets), G, int(tokens_per_tile),
          int(group_offsets is None if weights_first is None else weights_first), int(k_splits),
          _ptr(torch.empty(k_splits, M, N, dtype=torch.float32, device=out.device)) if k_splits > 1 else None,
@@ -829,17 +928,26 @@ def gemm_tc2(x, w, out, *, bias=None, accumulate=False, gated=False, status=None
     CTAs of a cluster, each fetching half of the tile's operands).  For prompt-sized dense products."""
     M, N = out.shape
     K = x.shape[1]
+    gated, lim, alpha = _gate_args(gated)
     if w.dim() != 2 or w.shape[0] != (2 * N if gated else N) or w.shape[1] != K or x.shape[0] != M:
         raise KernelError(f"gemm_tc2 shapes do not agree: x {tuple(x.shape)} w {tuple(w.shape)} out {tuple(out.shape)}")
     call("fx_gemm_tc2", _ptr(x), _rows(x), _ptr(w), w.stride(0), w.shape[0], _ptr(bias), code(bias) if bias is not None else 0,
-         _ptr(out), code(out), _rows(out), int(accumulate), M, N, K, int(gated), N if gated else 0, _ptr(status),
-         stream if stream is not None else stream_ptr())
+         _ptr(out), code(out), _rows(out), int(accumulate), M, N, K, int(gated), N if gated else 0, lim, alpha,
+         _ptr(status), stream if stream is not None else stream_ptr())
     return out
 
 
 def gather_rows(x, rows, out, stream=None):
     call("fx_gather_rows", _ptr(x), _rows(x), _ptr(rows), _ptr(out), _rows(out), code(x), out.shape[0], x.shape[1],
          stream if stream is not None else stream_ptr())
+    return out
+
+
+def gather_rows_scaled(x, rows, inv_perm, weights, out, stream=None):
+    """out[r] = w * x[rows[r]], w the routing weight of the (token, rank) pair whose row in expert order is r
+    (``inv_perm`` [T, top_k] gives each pair's row, ``weights`` [T, top_k] its weight)."""
+    call("fx_gather_rows_scaled", _ptr(x), _rows(x), _ptr(rows), _ptr(inv_perm), _ptr(weights), weights.shape[1],
+         _ptr(out), _rows(out), code(x), out.shape[0], x.shape[1], stream if stream is not None else stream_ptr())
     return out
 
 
@@ -902,7 +1010,7 @@ def gated_linear(x, w_gu, out, *, status=None, stream=None, activation="silu"):
     (``activation``): picks the kernel as :func:`linear` does; the gate|up intermediate reaches memory only on the
     CUDA-core path."""
     T, I = out.shape
-    gated = 1 + gate_code(activation)     # the kernels' argument: 0 plain, 1 SiLU gate, 2 ReLU gate
+    gated = gated_arg(activation)     # the kernels' argument: 0 plain, 1 SiLU gate, 2 ReLU gate, (3, limit, alpha)
     if T <= SKINNY_MAX_TOKENS and tc_ok(x, w_gu) and swap_better(T, 2 * I, x.shape[1]):
         return gemm_tc_swap(x, w_gu, out, gated=gated, status=status, stream=stream)
     if T <= SKINNY_MAX_TOKENS and skinny_ok(x, w_gu):
@@ -923,17 +1031,20 @@ def combine_norm_ok(h, y) -> bool:
     return y.dtype in _CODES and H % vw == 0 and H // vw <= 4 * 256
 
 
-def moe_combine(h, y, inv_perm, topk_w, shared=None, shared_gate_logit=None, stream=None, norm=None):
+def moe_combine(h, y, inv_perm, topk_w, shared=None, shared_gate_logit=None, stream=None, norm=None, top_k=None):
     """h[t] += sum_k topk_w[t, k] * y[inv_perm[t, k]] (+ sigmoid(gate logit) * shared[t]).  ``norm`` = (weight, eps,
-    out): also out[t] = rmsnorm(h[t]) * weight on the new rows, in the same kernel (see :func:`combine_norm_ok`)."""
+    out): also out[t] = rmsnorm(h[t]) * weight on the new rows, in the same kernel (see :func:`combine_norm_ok`).
+    ``topk_w`` None (then ``top_k`` says how many rows a token has): the rows are added as they are, for experts
+    whose routing weight went into their input."""
     T, H = h.shape
+    top_k = topk_w.shape[1] if topk_w is not None else int(top_k)
     if norm is not None:
         w, eps, out = norm
-        call("fx_moe_combine_norm", _ptr(h), _ptr(y), code(y), _ptr(inv_perm), _ptr(topk_w), topk_w.shape[1],
+        call("fx_moe_combine_norm", _ptr(h), _ptr(y), code(y), _ptr(inv_perm), _ptr(topk_w), top_k,
              _ptr(shared), _ptr(shared_gate_logit), shared_gate_logit.stride(0) if shared_gate_logit is not None else 0,
              T, H, _ptr(w), code(w), float(eps), _ptr(out), stream if stream is not None else stream_ptr())
         return out
-    call("fx_moe_combine", _ptr(h), _ptr(y), code(y), _ptr(inv_perm), _ptr(topk_w), topk_w.shape[1], _ptr(shared),
+    call("fx_moe_combine", _ptr(h), _ptr(y), code(y), _ptr(inv_perm), _ptr(topk_w), top_k, _ptr(shared),
          _ptr(shared_gate_logit), shared_gate_logit.stride(0) if shared_gate_logit is not None else 0, T, H, stream if stream is not None else stream_ptr())
 
 
@@ -978,3 +1089,21 @@ def sample(work, temperature, top_k, top_p, draw, out, stream=None):
     call("fx_sample", _ptr(work), _rows(work), n, V, _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(draw), _ptr(out),
          stream if stream is not None else stream_ptr())
     return out
+
+
+def grouped_linear(x, w, out, offsets, active, rows_per_group: int, *, status=None, stream=None):
+    """out[r] = x[r] . w[g]^T for the rows r of group g (``offsets`` int32 [G + 1] on the device, rows sorted by
+    group; ``w`` [G, N, K]; ``out`` may have a wider row stride than N).  ``active`` lists the groups that have rows
+    (int32, then -1), ``rows_per_group`` is the mean number of rows a group has, by which the kernel is chosen as the
+    experts' products choose theirs."""
+    T = x.shape[0]
+    G, N, K = w.shape
+    if tc_ok(x, w) and K % 8 == 0 and N % 8 == 0 and G <= TC_MAX_GROUPS and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0:
+        if rows_per_group > 16 or G > TC_SWAP_MAX_GROUPS:
+            return gemm_tc(x, w, out, group_offsets=offsets, status=status, stream=stream)
+        if T >= 8:
+            return gemm_tc_swap(x, w, out, group_offsets=offsets, tokens_per_tile=32 if rows_per_group <= 8 else 64,
+                                weights_first=True, status=status, stream=stream)
+    if rows_per_group <= SKINNY_MAX_TOKENS and skinny_ok(x, w) and active is not None:
+        return gemm_skinny(x, w, out, group_offsets=offsets, active_groups=active, tokens_hint=rows_per_group, stream=stream)
+    return gemm(x, w, out, group_offsets=offsets, stream=stream)

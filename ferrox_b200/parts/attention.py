@@ -16,7 +16,7 @@ import math
 import numpy as np
 import torch
 
-from ..cache.specs import CacheSpec, KvCacheSpec
+from ..cache.specs import CacheSpec, KvCacheSpec, PagedSpec, PagedTensorSpec
 from ..kernels import ops
 from ..weights.loader import TensorDecl
 from .base import Mixer, build_part, register_part
@@ -85,6 +85,25 @@ class GqaAttention(Mixer):
         self.position = build_part(s.position if s.position is not None else NoPositionSpec())
         self.q_size = s.n_heads * s.head_dim
         self.kv_size = s.n_kv_heads * s.head_dim
+        # Queries and keys normed per head, a query temperature, a distance bias, or values of another width than
+        # the keys: the general form (its own step between projection and attention, its own attention kernels).
+        self.value_dim = int(getattr(s, "value_dim", None) or s.head_dim)
+        self.qk_norm = getattr(s, "qk_norm", None)
+        self.temperature = getattr(s, "query_temperature", None)
+        self.slopes_spec = getattr(s, "distance_slopes", None)
+        self.general = bool(self.qk_norm or self.temperature or self.slopes_spec or self.value_dim != s.head_dim)
+        self.v_size = s.n_kv_heads * self.value_dim
+        self.o_size = s.n_heads * self.value_dim
+        if self.general:
+            if s.position is not None and not isinstance(s.position, NoPositionSpec):
+                raise ValueError("attention with normed queries and keys, a query temperature, a distance bias or its "
+                                 "own value width takes no rotary position encoding")
+            if s.tied_values or s.softcap:
+                raise ValueError("the general attention form has neither tied values nor a soft cap")
+            if self.slopes_spec is not None and len(self.slopes_spec) != s.n_heads:
+                raise ValueError("distance_slopes: one slope per head")
+            if self.temperature is not None and int(self.temperature[1]) < 1:
+                raise ValueError("query_temperature: 'every' is a positive number of positions")
         self.scale = s.softmax_scale if s.softmax_scale is not None else 1.0 / math.sqrt(s.head_dim)
         self.softcap = float(s.softcap) if s.softcap else None
         if self.softcap is not None and self.softcap < 0:
@@ -98,14 +117,21 @@ class GqaAttention(Mixer):
         self._qkv_keys = ("q", "k", "k") if s.tied_values else ("q", "k", "v")
 
     def cache_spec(self):
-        return CacheSpec(paged=KvCacheSpec(self.spec.n_kv_heads, self.spec.head_dim, self.spec.window))
+        s = self.spec
+        if self.value_dim != s.head_dim:
+            return CacheSpec(paged=PagedSpec((PagedTensorSpec("k", (s.n_kv_heads, s.head_dim), lead_dims=1),
+                                              PagedTensorSpec("v", (s.n_kv_heads, self.value_dim), lead_dims=1)), s.window))
+        return CacheSpec(paged=KvCacheSpec(s.n_kv_heads, s.head_dim, s.window))
 
     def tensor_decls(self):
         s, n = self.spec, self._names
-        sizes = dict(q=self.q_size, k=self.kv_size, v=self.kv_size)
+        sizes = dict(q=self.q_size, k=self.kv_size, v=self.v_size)
         keys = sorted(set(self._qkv_keys))
         d = [TensorDecl(n[key], (sizes[key], s.hidden)) for key in keys]
-        d.append(TensorDecl(n["o"], (s.hidden, self.q_size)))
+        d.append(TensorDecl(n["o"], (s.hidden, self.o_size)))
+        if self.qk_norm:
+            d += [TensorDecl(s.prefix + self.qk_norm[0], (s.head_dim,), init="ones"),
+                  TensorDecl(s.prefix + self.qk_norm[1], (s.head_dim,), init="ones")]
         if s.qkv_bias:
             d += [TensorDecl(n[key + "_bias"], (sizes[key],)) for key in keys]
         return d
@@ -123,6 +149,13 @@ class GqaAttention(Mixer):
             self.b_qkv = torch.cat([b.to(bdt) for b in bs]).contiguous()
         self.w_o = src.get(n["o"])
         self.position.load(src, rt)
+        self.q_norm_w = self.k_norm_w = self.slopes = None
+        if self.qk_norm:
+            ws = [src.get(self.spec.prefix + self.qk_norm[0]), src.get(self.spec.prefix + self.qk_norm[1])]
+            dt = _common_dtype(ws)
+            self.q_norm_w, self.k_norm_w = (w.to(dt).contiguous() for w in ws)
+        if self.slopes_spec is not None:
+            self.slopes = torch.tensor([float(x) for x in self.slopes_spec], dtype=torch.float32, device=rt.device)
         # zeroed scratch of the decode attention kernel that merges its own key ranges (it leaves it zeroed)
         self._range_counters = (torch.zeros(RANGE_COUNTERS, dtype=torch.int32, device=rt.device)
                                 if rt.device.type == "cuda" else None)
@@ -138,6 +171,8 @@ class GqaAttention(Mixer):
 
     def forward_into(self, x, out, batch, cache, accumulate=False):
         """out (+)= Wo . attention: ``out`` is the residual stream (accumulate) or a 32-bit buffer of its shape."""
+        if self.general:
+            return self._forward_general(x, out, batch, cache, accumulate)
         h = out
         s = self.spec
         T = x.shape[0]
@@ -209,6 +244,34 @@ class GqaAttention(Mixer):
         # (the attention's last blocks only add up key ranges: the memory system is idle under them)
         ops.linear(attn, self.w_o, h, accumulate=accumulate, status=batch.status, stream=batch.stream,
                    after_short_kernel=True)
+
+
+    def _forward_general(self, x, out, batch, cache, accumulate):
+        """The form with normed queries and keys, a query temperature, a distance bias, values of their own
+        width: fused [q | k | v] product; one kernel norms q and k per head, applies the temperature and stores k and
+        v; attention with the bias; output product."""
+        s = self.spec
+        T, D, V = x.shape[0], s.head_dim, self.value_dim
+        qkv = self.rt.empty(T, self.q_size + self.kv_size + self.v_size)
+        ops.linear(x, self.w_qkv, qkv, bias=self.b_qkv, status=batch.status, stream=batch.stream, after_short_kernel=True)
+        eps = self.qk_norm[2] if self.qk_norm else 0.0
+        ops.qk_norm_store(qkv, batch.positions, batch.token_seq, batch.seq_slot, self.q_norm_w, self.k_norm_w, eps,
+                          self.temperature, cache.k, cache.v, cache.block_table, cache.page_size, s.n_heads, s.n_kv_heads,
+                          D, V, write_cache=cache.writes, status=batch.status, stream=batch.stream)
+        attn = self.rt.empty(T, self.o_size)
+        general_attention(qkv, qkv.stride(0), D, cache.k, cache.v, D, V, attn, attn.stride(0), V, batch, cache,
+                          s.n_heads, s.n_kv_heads, D, V, s.window, self.scale, self.slopes, self.rt)
+        ops.linear(attn, self.w_o, out, accumulate=accumulate, status=batch.status, stream=batch.stream,
+                   after_short_kernel=True)
+
+
+def general_attention(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, out, ldo, ldoh, batch, cache, n_heads, n_kv_heads,
+                      key_dim, value_dim, window, scale, slopes, rt):
+    """Attention over pages in its general form (keys and values of different widths, strided queries and outputs, an
+    optional distance bias), by the kernel that fits the step."""
+    ops.paged_attention_ex(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, cache.block_table, cache.page_size, batch.positions,
+                           batch.token_seq, batch.seq_slot, out, ldo, ldoh, n_heads, n_kv_heads, key_dim, value_dim,
+                           window, scale, slopes=slopes, stream=batch.stream)
 
 
 register_part("gqa_attention", GqaAttention, replace=True)

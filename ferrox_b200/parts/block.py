@@ -59,6 +59,55 @@ class PreNormBlock(Block):
         return None
 
 
+class ParallelBlock(Block):
+    """One norm, two sublayers that read it, one residual addition each:
+
+        x = norm1(h);  h += mixer(x);  h += ffn(x)
+
+    (``ffn`` None: the layer ends after the mixer.)  The sum h + (mixer + ffn) is made in 32 bits in the stream."""
+
+    passes_norm = True
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.norm1 = build_part(spec.norm1)
+        self.mixer = build_part(spec.mixer)
+        self.ffn = build_part(spec.ffn) if spec.ffn is not None else None
+
+    def _parts(self):
+        return [p for p in (self.norm1, self.mixer, self.ffn) if p is not None]
+
+    def tensor_decls(self):
+        return [d for p in self._parts() for d in p.tensor_decls()]
+
+    def load(self, src, rt):
+        super().load(src, rt)
+        for part in self._parts():
+            part.load(src, rt)
+
+    def reset_after_fault(self):
+        for part in self._parts():
+            part.reset_after_fault()
+
+    @property
+    def graph_safe(self):
+        return all(p.graph_safe for p in self._parts())
+
+    def forward(self, h, batch, cache, x=None, then_norm=None):
+        if x is None:
+            with ops.trace_scope("norm"):
+                x = self.norm1.forward(h)
+        with ops.trace_scope("mixer"):
+            self.mixer.forward_add(x, h, batch, cache)
+        if self.ffn is None:
+            return None
+        with ops.trace_scope("feed-forward"):
+            if then_norm is not None and self.ffn.fuses_norm:
+                return self.ffn.forward_add(x, h, batch, then_norm=then_norm)
+            self.ffn.forward_add(x, h, batch)
+        return None
+
+
 class SandwichNormBlock(Block):
     """A norm before and after each sublayer,
 
@@ -149,3 +198,4 @@ class SandwichNormBlock(Block):
 
 register_part("pre_norm", PreNormBlock, replace=True)
 register_part("sandwich_norm", SandwichNormBlock, replace=True)
+register_part("parallel", ParallelBlock, replace=True)

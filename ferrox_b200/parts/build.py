@@ -2,7 +2,7 @@
 from __future__ import annotations
 
 # importing the modules registers the parts that ship with the framework
-from . import attention, block, combine, linear_state, mlp, moe, norm, position  # noqa: F401
+from . import attention, block, combine, latent_attention, linear_state, mlp, moe, norm, position  # noqa: F401
 from .model import DecoderModel
 
 

@@ -5,6 +5,12 @@
     y = sum_k w_k * down_e( silu(gate_e x) * (up_e x) ), summed in rank order;
     y += sigmoid(w_sg . x) * shared(x)   (the gate only if the checkpoint has it).
 
+Variants the spec can ask for: ``scores="sigmoid"`` (the weights are sigmoid(logit) of the chosen experts; the
+choice is the same, both scores rise with the logit); ``weight_on_input`` (y = sum_k expert_e(w_k x): the rows are
+scaled while they are brought into expert order, and the combination adds the experts' outputs as they are);
+``activation`` (what the gate passes through, e.g. the clamped unit with its limit; the shared expert may have its
+own constants).
+
 Reference: router crates/ferrox-moe/src/lib.rs:333-355, expert :619-659, combine
 :735-752, shared expert and its sigmoid gate crates/ferrox-models/src/decoder.rs:
 2660-2681 and (batched) :1037-1093; tokens bucketed by expert :2792-2890.
@@ -45,20 +51,42 @@ def expert_tile_tokens(T: int, K: int, E: int):
 class SoftmaxTopkMoe(FeedForward):
     graph_safe = True
     fuses_norm = True
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        s = spec
+        self.scores = getattr(s, "scores", "softmax")
+        if self.scores not in ("softmax", "sigmoid"):
+            raise ValueError(f"router scores {self.scores!r}: softmax or sigmoid")
+        self.weight_on_input = bool(getattr(s, "weight_on_input", False))
+        self.activation = getattr(s, "activation", "silu")
+        self.shared_activation = getattr(s, "shared_activation", None) or self.activation
+        self._gated = ops.gated_arg(self.activation)      # unknown activations fail here, by name
+        ops.gated_arg(self.shared_activation)
+        self._route_mode = int(bool(s.norm_topk_prob)) | (2 if self.scores == "sigmoid" else 0)
+        router, expert, shared = getattr(s, "tensor_names", None) or (
+            "gate.weight", "experts.{e}.{part}_proj.weight", "shared_expert.{part}_proj.weight")
+        p = s.prefix
+        self._router_name = p + router
+        self._expert_name = lambda e, part: p + expert.format(e=e, part=part)
+        self._shared_name = lambda part: p + shared.format(part=part)
+        if not 1 <= s.top_k <= s.n_experts:
+            raise ValueError(f"top_k={s.top_k} of {s.n_experts} experts")
+
     def tensor_decls(self):
         s, p = self.spec, self.spec.prefix
-        d = [TensorDecl(p + "gate.weight", (s.n_experts, s.hidden))]
+        d = [TensorDecl(self._router_name, (s.n_experts, s.hidden))]
         for e in range(s.n_experts):
             d += [
-                TensorDecl(p + f"experts.{e}.gate_proj.weight", (s.expert_intermediate, s.hidden)),
-                TensorDecl(p + f"experts.{e}.up_proj.weight", (s.expert_intermediate, s.hidden)),
-                TensorDecl(p + f"experts.{e}.down_proj.weight", (s.hidden, s.expert_intermediate)),
+                TensorDecl(self._expert_name(e, "gate"), (s.expert_intermediate, s.hidden)),
+                TensorDecl(self._expert_name(e, "up"), (s.expert_intermediate, s.hidden)),
+                TensorDecl(self._expert_name(e, "down"), (s.hidden, s.expert_intermediate)),
             ]
         if s.shared_intermediate > 0:
             d += [
-                TensorDecl(p + "shared_expert.gate_proj.weight", (s.shared_intermediate, s.hidden)),
-                TensorDecl(p + "shared_expert.up_proj.weight", (s.shared_intermediate, s.hidden)),
-                TensorDecl(p + "shared_expert.down_proj.weight", (s.hidden, s.shared_intermediate)),
+                TensorDecl(self._shared_name("gate"), (s.shared_intermediate, s.hidden)),
+                TensorDecl(self._shared_name("up"), (s.shared_intermediate, s.hidden)),
+                TensorDecl(self._shared_name("down"), (s.hidden, s.shared_intermediate)),
             ]
             if s.shared_gate:
                 d.append(TensorDecl(p + "shared_expert_gate.weight", (1, s.hidden), optional=True))
@@ -67,23 +95,21 @@ class SoftmaxTopkMoe(FeedForward):
     def load(self, src, rt):
         super().load(src, rt)
         s, p = self.spec, self.spec.prefix
-        self.w_router = src.get(p + "gate.weight")
+        self.w_router = src.get(self._router_name)
         E, I, H = s.n_experts, s.expert_intermediate, s.hidden
         # If any expert tensor is stored in 32 bits, the packed buffers are 32-bit.
-        names = [p + f"experts.{e}.{n}_proj.weight" for e in range(E) for n in ("gate", "up", "down")]
+        names = [self._expert_name(e, n) for e in range(E) for n in ("gate", "up", "down")]
         dt = torch.float32 if any(src.dtype_of(n) == torch.float32 for n in names) else rt.dtype
         self.w_gu = torch.empty(E, 2 * I, H, dtype=dt, device=rt.device)
         self.w_down = torch.empty(E, H, I, dtype=dt, device=rt.device)
         for e in range(E):
-            self.w_gu[e, :I].copy_(src.get(p + f"experts.{e}.gate_proj.weight"))
-            self.w_gu[e, I:].copy_(src.get(p + f"experts.{e}.up_proj.weight"))
-            self.w_down[e].copy_(src.get(p + f"experts.{e}.down_proj.weight"))
+            self.w_gu[e, :I].copy_(src.get(self._expert_name(e, "gate")))
+            self.w_gu[e, I:].copy_(src.get(self._expert_name(e, "up")))
+            self.w_down[e].copy_(src.get(self._expert_name(e, "down")))
         self.w_shared_gu = self.w_shared_down = self.w_shared_gate = None
         if s.shared_intermediate > 0:
-            self.w_shared_gu = pack_gate_up(
-                src.get(p + "shared_expert.gate_proj.weight"), src.get(p + "shared_expert.up_proj.weight")
-            )
-            self.w_shared_down = src.get(p + "shared_expert.down_proj.weight")
+            self.w_shared_gu = pack_gate_up(src.get(self._shared_name("gate")), src.get(self._shared_name("up")))
+            self.w_shared_down = src.get(self._shared_name("down"))
             if s.shared_gate and src.has(p + "shared_expert_gate.weight"):
                 self.w_shared_gate = src.get(p + "shared_expert_gate.weight").reshape(1, H).contiguous()
         # router rows and the shared expert's gate row share one product: [E (+1), H]
@@ -101,7 +127,7 @@ class SoftmaxTopkMoe(FeedForward):
         s, rt = self.spec, self.rt
         T, Is = x.shape[0], s.shared_intermediate
         sact = rt.empty(T, Is)
-        ops.gated_linear(x, self.w_shared_gu, sact, status=batch.status, stream=st)
+        ops.gated_linear(x, self.w_shared_gu, sact, status=batch.status, stream=st, activation=self.shared_activation)
         shared = rt.empty(T, s.hidden)
         ops.linear(sact, self.w_shared_down, shared, status=batch.status, stream=st)
         return shared
@@ -121,6 +147,7 @@ class SoftmaxTopkMoe(FeedForward):
         # A decode step of a few tokens: the router's product, the routing and the rows in expert order come from ONE
         # kernel (three dependent launches otherwise, each a few microseconds of waiting for the one before).
         fused = ops.route_fused_ok(x, self.w_route, E, K)
+        mode, gated, scaled = self._route_mode, self._gated, self.weight_on_input
         tc = ops.tc_ok(x, self.w_gu) and I % 8 == 0 and E <= ops.TC_MAX_GROUPS
         tiles = expert_tile_tokens(T, K, E) if tc and T >= SWAP_MIN_TOKENS and E <= ops.TC_SWAP_MAX_GROUPS else None
         small = tiles is None and T <= ops.SKINNY_MAX_TOKENS and ops.skinny_ok(x, self.w_gu) and I % 32 == 0
@@ -150,22 +177,26 @@ class SoftmaxTopkMoe(FeedForward):
             # The cluster's kernel goes first: it needs eight free SMs of one GPC at once, which it finds now and would
             # not find once the shared expert's weight-streaming kernels (enqueued right after it, waiting only for what
             # was before it) fill every SM.
-            xp = rt.empty(T * K, H) if tiles is not None else None
-            ops.route_fused(x, self.w_route, logits, K, s.norm_topk_prob, ids, weights, offsets, src_token, inv_perm, active,
+            xp = rt.empty(T * K, H) if tiles is not None and not scaled else None
+            ops.route_fused(x, self.w_route, logits, K, mode, ids, weights, offsets, src_token, inv_perm, active,
                             n_experts=E, xp_out=xp, stream=st)
             if overlap:
                 shared = self._shared_on_side(x, batch)
         elif T <= ops.ROUTE_SMALL_MAX_TOKENS and E <= ops.ROUTE_SMALL_MAX_EXPERTS:
             ops.linear(x, self.w_route, logits, status=batch.status, stream=st)
-            ops.route_small(logits, K, s.norm_topk_prob, ids, weights, offsets, src_token, inv_perm, active,
+            ops.route_small(logits, K, mode, ids, weights, offsets, src_token, inv_perm, active,
                             n_experts=E, stream=st)
         else:
             ops.linear(x, self.w_route, logits, status=batch.status, stream=st)
-            ops.route(logits, K, s.norm_topk_prob, ids, weights, self._scratch, offsets, src_token, inv_perm, active,
+            ops.route(logits, K, mode, ids, weights, self._scratch, offsets, src_token, inv_perm, active,
                       n_experts=E, stream=st)
 
         act = rt.empty(T * K, I)
         y = rt.empty(T * K, H)
+        if scaled:
+            # the routing weight goes into the expert's input: rows scaled on their way into expert order
+            xp = rt.empty(T * K, H)
+            ops.gather_rows_scaled(x, src_token, inv_perm, weights, xp, stream=st)
         if tiles is not None:
             # a few rows for each expert: rows in expert order, then features in the lanes of the tensor-core tiles
             # and the expert's rows in their columns
@@ -174,25 +205,27 @@ class SoftmaxTopkMoe(FeedForward):
                 ops.gather_rows(x, src_token, xp, stream=st)
             # (the offsets were written by the routing, before the gather: both products may fetch weights early;
             # when one kernel did both, the first product waits for it before it reads the offsets)
-            ops.gemm_tc_swap(xp, self.w_gu, act, gated=True, group_offsets=offsets, tokens_per_tile=tiles[0],
-                             weights_first=not fused, status=batch.status, stream=st)
+            ops.gemm_tc_swap(xp, self.w_gu, act, gated=gated, group_offsets=offsets, tokens_per_tile=tiles[0],
+                             weights_first=not fused and not scaled, status=batch.status, stream=st)
             ops.gemm_tc_swap(act, self.w_down, y, group_offsets=offsets, tokens_per_tile=tiles[1],
                              weights_first=True, status=batch.status, stream=st)
         elif small:
             # very few tokens: every expert that was chosen is streamed once, gate/up fused with SiLU
-            ops.gemm_skinny(x, self.w_gu, act, gated=True, x_rows=src_token, group_offsets=offsets,
-                            active_groups=active, tokens_hint=T, stream=st)
+            ops.gemm_skinny(xp if scaled else x, self.w_gu, act, gated=gated, x_rows=None if scaled else src_token,
+                            group_offsets=offsets, active_groups=active, tokens_hint=T, stream=st)
             ops.gemm_skinny(act, self.w_down, y, group_offsets=offsets, active_groups=active, tokens_hint=T, stream=st)
         elif big:
             # many tokens: bring them into expert order once, then grouped tensor-core products
-            xp = rt.empty(T * K, H)
-            ops.gather_rows(x, src_token, xp, stream=st)
-            ops.gemm_tc(xp, self.w_gu, act, gated=True, group_offsets=offsets, status=batch.status, stream=st)
+            if xp is None:
+                xp = rt.empty(T * K, H)
+                ops.gather_rows(x, src_token, xp, stream=st)
+            ops.gemm_tc(xp, self.w_gu, act, gated=gated, group_offsets=offsets, status=batch.status, stream=st)
             ops.gemm_tc(act, self.w_down, y, group_offsets=offsets, status=batch.status, stream=st)
         else:
             gu = rt.empty(T * K, 2 * I)
-            ops.gemm(x, self.w_gu, gu, a_rows=src_token, group_offsets=offsets, stream=st)
-            ops.silu_mul(gu, act, stream=st)
+            ops.gemm(xp if scaled else x, self.w_gu, gu, a_rows=None if scaled else src_token, group_offsets=offsets,
+                     stream=st)
+            ops.silu_mul(gu, act, stream=st, activation=self.activation)
             ops.gemm(act, self.w_down, y, group_offsets=offsets, stream=st)
 
         gate_logit = None
@@ -207,8 +240,9 @@ class SoftmaxTopkMoe(FeedForward):
         rms = then_norm.as_rms() if then_norm is not None else None
         if rms is not None and ops.combine_norm_ok(h, y):
             out = rt.empty(T, H)
-            return ops.moe_combine(h, y, inv_perm, weights, shared, gate_logit, stream=st, norm=(rms[0], rms[1], out))
-        ops.moe_combine(h, y, inv_perm, weights, shared, gate_logit, stream=st)
+            return ops.moe_combine(h, y, inv_perm, None if scaled else weights, shared, gate_logit, stream=st,
+                                   norm=(rms[0], rms[1], out), top_k=K)
+        ops.moe_combine(h, y, inv_perm, None if scaled else weights, shared, gate_logit, stream=st, top_k=K)
         return None
 
 

@@ -2,19 +2,31 @@
 (reference: crates/ferrox-core/src/matmul.rs:62-69,121-123)."""
 from __future__ import annotations
 
+import torch
+
 from ..kernels import ops
 from ..weights.loader import TensorDecl
 from .base import Norm, register_part
 
 
 class RmsNorm(Norm):
+    """``one_plus``: the stored weight lies around zero and the norm multiplies by 1 + w (added once, in 32 bits,
+    when the weights are loaded)."""
+
     graph_safe = True
+
+    def _name(self):
+        return getattr(self.spec, "name", None) or self.spec.prefix + "weight"
+
     def tensor_decls(self):
-        return [TensorDecl(self.spec.prefix + "weight", (self.spec.size,), init="ones")]
+        one_plus = getattr(self.spec, "one_plus", False)
+        return [TensorDecl(self._name(), (self.spec.size,), init="normal" if one_plus else "ones")]
 
     def load(self, src, rt):
         super().load(src, rt)
-        self.weight = src.get(self.spec.prefix + "weight")
+        self.weight = src.get(self._name())
+        if getattr(self.spec, "one_plus", False):
+            self.weight = (1.0 + self.weight.to(torch.float32)).contiguous()
 
     def forward(self, h, rows=None):
         n = h.shape[0] if rows is None else rows.numel()

@@ -24,6 +24,8 @@ class NormSpec:
     eps: float
     prefix: str  # tensor: <prefix>weight
     kind: str = "rms_norm"
+    name: Optional[str] = None  # the weight tensor's full name, where it is not <prefix>weight
+    one_plus: bool = False  # the stored weight lies around zero: the norm multiplies by 1 + w
 
 
 @dataclass(frozen=True)
@@ -79,6 +81,39 @@ class AttentionSpec:
     # and q_bias, k_bias, v_bias
     tensor_names: Optional[Tuple[Tuple[str, str], ...]] = None
     kind: str = "gqa_attention"
+    value_dim: Optional[int] = None  # width of a value head where it differs from head_dim
+    # queries and keys RMS-normed per head before anything else, with one weight vector [head_dim] each that all
+    # heads share: (name of q's weight after <prefix>, name of k's, eps)
+    qk_norm: Optional[Tuple[str, str, float]] = None
+    # (coef, every): the query at position p is multiplied by 1 + coef * ln(floor((p + 1) / every) + 1)
+    query_temperature: Optional[Tuple[float, int]] = None
+    # one slope per head: slope * (i - j) is taken off the score of key j for the query at position i
+    distance_slopes: Optional[Tuple[float, ...]] = None
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Attention whose keys and values are read out of one latent vector a position.  Per head ``head_dim`` plain
+    and ``rot_dim`` rotated query/key elements; a position stores the normed latent [kv_rank] and one rotated key
+    part [rot_dim] that all heads share; per head the plain key is uk . c and the value uv . c.  ``q_rank``: the
+    queries pass a normed latent of their own.  ``output_gate``: the heads' outputs are multiplied by sigmoid(g . x).
+    Tensors after <prefix>: q (or dq, dq.norm, uq), dkv, dkv.norm, uk, uv, g, o."""
+
+    hidden: int
+    n_heads: int
+    head_dim: int
+    rot_dim: int
+    value_dim: int
+    kv_rank: int
+    q_rank: Optional[int]
+    rotary_dims: int  # the leading elements of the rot_dim part that are rotated, on neighbouring pairs
+    rotary_base: float
+    window: Optional[int]
+    scale: float
+    output_gate: bool
+    norm_eps: float
+    prefix: str
+    kind: str = "latent_attention"
 
 
 @dataclass(frozen=True)
@@ -144,6 +179,14 @@ class MoeSpec:
     prefix: str  # tensors: <prefix>gate.weight, <prefix>experts.<e>.{gate,up,down}_proj.weight,
     #                       <prefix>shared_expert.{gate,up,down}_proj.weight, <prefix>shared_expert_gate.weight
     kind: str = "softmax_topk_moe"
+    scores: str = "softmax"  # what the router's logits become: softmax over all experts, or sigmoid of each
+    weight_on_input: bool = False  # the routing weight multiplies the expert's input instead of its output
+    # what the gate passes through: a name the kernels know, or (name, limit, alpha) for the clamped unit
+    activation: object = "silu"
+    shared_activation: object = None  # the shared expert's, where it differs
+    # names after <prefix> where a checkpoint spells them differently: (router, expert pattern with {e} and {part},
+    # shared pattern with {part}), part being gate, up or down
+    tensor_names: Optional[Tuple[str, str, str]] = None
 
 
 @dataclass(frozen=True)
@@ -155,6 +198,17 @@ class BlockSpec:
     norm2: object
     ffn: object
     kind: str = "pre_norm"
+
+
+@dataclass(frozen=True)
+class ParallelBlockSpec:
+    """One norm, both sublayers read its output: h += mixer(norm1(h)) + ffn(norm1(h)).  ``ffn`` None: no
+    feed-forward."""
+
+    norm1: object
+    mixer: object
+    ffn: Optional[object]
+    kind: str = "parallel"
 
 
 @dataclass(frozen=True)
