@@ -48,6 +48,15 @@ int fx_paged_attention_ex(const void* q, long ldq, long ldqh, const void* k_page
                           int n_heads, int n_kv_heads, int key_dim, int value_dim, int window, float scale, float softcap,
                           const float* slopes, void* stream);
 
+// the same contract in bfloat16 on the tensor cores (attention_general_mma.cu); items: int32 [n_items, 5] = (first flat
+// token, tokens, entry, first query head, heads) or nullptr (one token a tile, n_items = tokens)
+int fx_general_attention_ok(int key_dim, int value_dim, int alias);
+int fx_general_attention(const void* q, long ldq, long ldqh, const void* k_pages, const void* v_pages, long ldk, long ldv,
+                         const int* block_table, int table_width, int page_size, const int* positions,
+                         const int* token_seq, const int* seq_slot, const int* items, int n_items, void* out, long ldo,
+                         long ldoh, int n_heads, int n_kv_heads, int key_dim, int value_dim, int window, float scale,
+                         const float* slopes, void* stream);
+
 int fx_prefill_attention_tc(const void* q, long ldq, int n_tokens, const void* k_pages, const void* v_pages, int n_pages,
                             const int* block_table, int table_width, int page_size, const int* items, int n_items,
                             const int* seq_slot, void* out, long ldo, int n_heads, int n_kv_heads, int head_dim,

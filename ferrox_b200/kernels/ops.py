@@ -49,6 +49,9 @@ _SIGNATURES = {
     "fx_gather_rows_scaled": [_P, _L, _P, _P, _P, _I, _P, _L, _I, _I, _I, _P],
     "fx_paged_attention_ex": [_P, _L, _L, _P, _P, _L, _L, _I, _P, _I, _I, _P, _P, _P, _P, _L, _L, _I, _I, _I, _I, _I, _I, _F,
                               _F, _P, _P],
+    "fx_general_attention_ok": [_I, _I, _I],
+    "fx_general_attention": [_P, _L, _L, _P, _P, _L, _L, _P, _I, _I, _P, _P, _P, _P, _I, _P, _L, _L, _I, _I, _I, _I, _I, _F,
+                             _P, _P],
     "fx_qk_norm_store": [_P, _I, _L, _P, _P, _P, _P, _P, _I, _F, _F, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "fx_latent_prep": [_P, _L, _P, _L, _I, _P, _P, _P, _P, _I, _F, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P,
                        _P],
@@ -521,6 +524,53 @@ def paged_attention_ex(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, block_table, pa
          _ptr(block_table), block_table.shape[1], page_size, _ptr(positions), _ptr(token_seq), _ptr(seq_slot), _ptr(out),
          int(ldo), int(ldoh), T, n_heads, n_kv_heads, key_dim, value_dim, int(window or 0), float(scale),
          float(softcap or 0.0), _ptr(slopes), stream if stream is not None else stream_ptr())
+    return out
+
+
+GENERAL_TILE_ROWS = 64     # (token, head) pairs a tile of the tensor-core kernel of the general form holds
+
+
+def general_attention_ok(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, out, ldo, ldoh, key_dim, value_dim) -> bool:
+    """Whether :func:`general_attention` takes these operands (bfloat16, widths in steps of 16, 16-byte rows)."""
+    alias = int(v_pages.data_ptr() == k_pages.data_ptr() and ldv == ldk and value_dim <= key_dim)
+    return (q.dtype == torch.bfloat16 and k_pages.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+            and ldq % 8 == 0 and ldqh % 8 == 0 and ldk % 8 == 0 and ldv % 8 == 0 and ldo % 2 == 0 and ldoh % 2 == 0
+            and q.data_ptr() % 16 == 0 and k_pages.data_ptr() % 16 == 0 and v_pages.data_ptr() % 16 == 0
+            and out.data_ptr() % 4 == 0 and bool(_get("fx_general_attention_ok")(key_dim, value_dim, alias)))
+
+
+def general_attention_items(entries, n_heads: int, n_kv_heads: int):
+    """The work list of :func:`general_attention` for a step: int32 [n, 5] rows of (first flat token, tokens, entry,
+    first query head, heads).  ``entries``: the number of tokens of each entry, in the order of the flattened batch.
+    A tile holds up to GENERAL_TILE_ROWS (token, head) pairs: consecutive tokens of one entry times the heads (at
+    most that many) that share one kv head."""
+    import numpy as np
+
+    group = n_heads // n_kv_heads
+    n_h = min(group, GENERAL_TILE_ROWS)
+    per = max(1, GENERAL_TILE_ROWS // n_h)
+    out, flat = [], 0
+    for b, n in enumerate(entries):
+        for i in range(0, n, per):
+            nt = min(per, n - i)
+            for g in range(n_kv_heads):
+                for c in range(0, group, GENERAL_TILE_ROWS):
+                    out.append((flat + i, nt, b, g * group + c, min(GENERAL_TILE_ROWS, group - c)))
+        flat += n
+    return np.asarray(out, dtype=np.int32).reshape(-1, 5)
+
+
+def general_attention(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, block_table, page_size, positions, token_seq, seq_slot,
+                      items, out, ldo, ldoh, n_heads, n_kv_heads, key_dim, value_dim, window, scale, slopes=None,
+                      stream=None):
+    """:func:`paged_attention_ex` in bfloat16 on the tensor cores (see :func:`general_attention_ok`).  ``items``: the
+    device copy of :func:`general_attention_items`, or None when every entry brings one token (a tile a token and
+    kv head; nothing comes from the host, so a captured step replays unchanged)."""
+    n = items.shape[0] if items is not None else positions.numel()
+    call("fx_general_attention", _ptr(q), int(ldq), int(ldqh), _ptr(k_pages), _ptr(v_pages), int(ldk), int(ldv),
+         _ptr(block_table), block_table.shape[1], page_size, _ptr(positions), _ptr(token_seq), _ptr(seq_slot),
+         _ptr(items), n, _ptr(out), int(ldo), int(ldoh), n_heads, n_kv_heads, key_dim, value_dim, int(window or 0),
+         float(scale), _ptr(slopes), stream if stream is not None else stream_ptr())
     return out
 
 

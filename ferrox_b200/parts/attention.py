@@ -268,7 +268,20 @@ class GqaAttention(Mixer):
 def general_attention(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, out, ldo, ldoh, batch, cache, n_heads, n_kv_heads,
                       key_dim, value_dim, window, scale, slopes, rt):
     """Attention over pages in its general form (keys and values of different widths, strided queries and outputs, an
-    optional distance bias), by the kernel that fits the step."""
+    optional distance bias), by the kernel that fits the step: tiles of (token, head) pairs on the tensor cores
+    in bfloat16, a warp per (token, head) on the CUDA cores in 32-bit and for widths that are no multiple of 16."""
+    if ops.general_attention_ok(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, out, ldo, ldoh, key_dim, value_dim):
+        items = None
+        if batch.max_new > 1:
+            key = ("general attention items", n_heads, n_kv_heads)
+            items = batch.shared.get(key)
+            if items is None:
+                items = torch.from_numpy(ops.general_attention_items([len(e.tokens) for e in batch.entries], n_heads,
+                                                                     n_kv_heads)).to(batch.token_ids.device)
+                batch.shared[key] = items
+        return ops.general_attention(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, cache.block_table, cache.page_size,
+                                     batch.positions, batch.token_seq, batch.seq_slot, items, out, ldo, ldoh, n_heads,
+                                     n_kv_heads, key_dim, value_dim, window, scale, slopes=slopes, stream=batch.stream)
     ops.paged_attention_ex(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, cache.block_table, cache.page_size, batch.positions,
                            batch.token_seq, batch.seq_slot, out, ldo, ldoh, n_heads, n_kv_heads, key_dim, value_dim,
                            window, scale, slopes=slopes, stream=batch.stream)

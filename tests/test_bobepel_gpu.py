@@ -1,0 +1,434 @@
+"""The engine's Bobepel model against the plain implementation: every mechanism alone, then whole models under every
+way of cutting the work (whole prompts, a decoded tail, portions down to two tokens, mixed batches with pages and
+slots used again, long decoding, generation through the scheduler), in 32-bit and in bfloat16, on configurations
+that differ in every size, constant, in the order of layers and in which layers share weights."""
+import random
+
+import pytest
+import torch
+
+import plain_bobepel as pb
+import replay_util as ru
+from bobepel_configs import CONFIGS, make_folder
+from test_safepel_gpu import CUTS, MixerHarness, load_part, random_tensors, rel, run_in_cuts
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = {"float32": (torch.float32, 5e-5), "bfloat16": (torch.bfloat16, 3e-2)}
+
+
+def slopes(n_heads):
+    from ferrox_b200.models.bobepel import distance_slopes
+
+    return distance_slopes(n_heads)
+
+
+def attention_spec(hidden, H, G, D, V, scale, temp, window=None):
+    from ferrox_b200.parts.specs import AttentionSpec
+
+    return AttentionSpec(hidden=hidden, n_heads=H, n_kv_heads=G, head_dim=D, qkv_bias=False, position=None, window=window,
+                         prefix="m.", softmax_scale=scale, value_dim=V,
+                         tensor_names=(("q", "q"), ("k", "k"), ("v", "v"), ("o", "o")), qk_norm=("q.norm", "k.norm", 1e-6),
+                         query_temperature=temp, distance_slopes=slopes(H))
+
+
+def latent_spec(hidden, H, D, R, rot_dims, V, C, scale, window=None, q_rank=None, base=10000.0):
+    from ferrox_b200.parts.specs import LatentAttentionSpec
+
+    return LatentAttentionSpec(hidden=hidden, n_heads=H, head_dim=D, rot_dim=R, value_dim=V, kv_rank=C, q_rank=q_rank,
+                               rotary_dims=rot_dims, rotary_base=base, window=window, scale=scale,
+                               output_gate=q_rank is None, norm_eps=1e-6, prefix="m.")
+
+
+def inputs(hidden, lens, seed, dt, loud=None):
+    """Rows for each request, rounded to the engine's element type; ``loud`` = (request, position): that row 20
+    times as large, so that whether a later query sees it shows in the result."""
+    g = torch.Generator().manual_seed(seed)
+    xs = [torch.randn(n, hidden, generator=g) for n in lens]
+    if loud is not None:
+        xs[loud[0]][loud[1]] *= 20.0
+    return [x.to(dt).float() for x in xs]
+
+
+# ------------------------------------------------------------------ mechanisms alone
+@pytest.mark.parametrize("dtype", list(DTYPES))
+def test_norm_with_a_weight_around_zero(dtype):
+    from ferrox_b200.parts.specs import NormSpec
+
+    dt, tol = DTYPES[dtype]
+    g = torch.Generator().manual_seed(0)
+    for H in (72, 300):
+        spec = NormSpec(H, 3e-6, "n.", name="n.norm1", one_plus=True)
+        w = {"n.norm1": (torch.randn(H, generator=g) * 0.3).to(torch.bfloat16)}
+        part, rt = load_part(spec, w, dt)
+        h = torch.randn(7, H, generator=g) * 4 + 2.5
+        got = part.forward(h.to(DEV))
+        assert rel(got, pb.norm_one_plus(h, w["n.norm1"].float(), 3e-6)) < tol
+
+
+@pytest.mark.parametrize("top,shared", [(1, True), (2, True), (3, False), (5, True)])
+@pytest.mark.parametrize("tokens", [1, 5, 40, 300])
+@pytest.mark.parametrize("dtype", list(DTYPES))
+def test_experts_weighted_on_their_input_alone(dtype, tokens, top, shared):
+    """The chosen experts' sigmoid scores multiply the experts' INPUT; the gate is clamped from above, the up value
+    from both sides (limits small enough to bite); at every step size the product kernels change."""
+    from ferrox_b200.engine.batch import StepEntry, flatten
+    from ferrox_b200.kernels import ops
+    from ferrox_b200.parts.specs import MoeSpec
+
+    dt, tol = DTYPES[dtype]
+    hidden, E, I, Is = 64, 5, 32, 48
+    spec = MoeSpec(hidden=hidden, n_experts=E, top_k=top, expert_intermediate=I, shared_intermediate=Is if shared else 0,
+                   norm_topk_prob=False, shared_gate=False, prefix="f.", scores="sigmoid", weight_on_input=True,
+                   activation=("clamped_swish", 0.6, 1.702), shared_activation=("clamped_swish", 0.9, 1.702) if shared else None,
+                   tensor_names=("router", "e{e}.{part}", "shared.{part}"))
+    w = random_tensors(spec, seed=tokens + top, std=0.2)
+    part, rt = load_part(spec, w, dt)
+    x = inputs(hidden, [tokens], 5, dt)[0]
+    f = {"router": {"experts": E, "top": top}, "expert": {"ff": I, "limit": 0.6},
+         "shared": {"ff": Is, "limit": 0.9} if shared else None}
+    wf = {k: v.float() for k, v in w.items()}
+    want = pb.feed_forward(x, f, wf, "f.")
+    # the test can tell: weights on the outputs instead, or no clamp, give something else
+    idx, sc, _ = pb.router(x, wf, "f.", top)
+    wrong = sum(sc[:, r:r + 1] * torch.stack([pb.expert(x[t:t + 1], wf, f"f.e{int(idx[t, r])}.", 0.6)[0] for t in range(tokens)])
+                for r in range(top))
+    if shared:
+        wrong = wrong + pb.expert(x, wf, "f.shared.", 0.9)
+    assert rel(wrong, want) > 0.05
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    batch = flatten([StepEntry(0, [0] * tokens, start=0)], torch.device(DEV), status, ops.stream_ptr())
+    h = torch.zeros(tokens, hidden, dtype=torch.float32, device=DEV)
+    part.forward_add(x.to(DEV).to(dt), h, batch)
+    torch.cuda.synchronize()
+    if dtype == "bfloat16":
+        # a position whose router separates the last chosen expert from the next by less than bfloat16 rounding may
+        # rightly choose the other one: leave those rows out, and require them to be few
+        s = torch.sigmoid(x @ wf["f.router"].T).sort(dim=-1, descending=True).values
+        clear = (s[:, top - 1] - s[:, top]) > 0.02 if top < E else torch.ones(tokens, dtype=torch.bool)
+        assert clear.float().mean() > 0.7
+        assert rel(h.cpu()[clear], want[clear]) < tol
+    else:
+        assert rel(h, want) < tol
+
+
+@pytest.mark.parametrize("cut", list(CUTS))
+@pytest.mark.parametrize("H,G,D,V,page", [(4, 2, 32, 48, 4), (3, 3, 20, 12, 8), (8, 1, 128, 64, 64), (6, 1, 24, 40, 16)])
+@pytest.mark.parametrize("dtype", list(DTYPES))
+def test_attention_with_normed_heads_temperature_and_distance_bias_alone(dtype, H, G, D, V, page, cut):
+    dt, tol = DTYPES[dtype]
+    hidden = 64
+    spec = attention_spec(hidden, H, G, D, V, 0.3, (0.5, 7))
+    w = random_tensors(spec, seed=H + D, std=0.25)
+    part, rt = load_part(spec, w, dt)
+    xs = inputs(hidden, (150, 37), 3, dt, loud=(0, 2))
+    m = dict(heads=H, kv_heads=G, dim=D, vdim=V, scale=0.3, q_temp={"coef": 0.5, "every": 7})
+    wf = {k: v.float() for k, v in w.items()}
+    want = [pb.mixer_attention(x, m, wf, "m.", 1e-6) for x in xs]
+    got = run_in_cuts(MixerHarness(part, rt, hidden, page_size=page, n_pages=256 // page + 8), xs, CUTS[cut])
+    for a, b in zip(got, want):
+        assert rel(a, b) < tol
+
+
+@pytest.mark.parametrize("dtype", list(DTYPES))
+def test_attention_reads_a_key_far_back_and_its_bias_is_the_distance(dtype):
+    """One early row is loud (its value 20 times the others'): hundreds of positions later the heads with small
+    slopes still read it and the heads with large slopes do not; with slope * j instead of slope * (i - j), or
+    without the temperature, the plain implementation itself gives something else."""
+    dt, tol = DTYPES[dtype]
+    hidden, H, G, D, V = 64, 8, 2, 32, 32
+    spec = attention_spec(hidden, H, G, D, V, 0.4, (0.8, 16))
+    w = random_tensors(spec, seed=1, std=0.25)
+    part, rt = load_part(spec, w, dt)
+    xs = inputs(hidden, (700, 9), 4, dt, loud=(0, 3))
+    m = dict(heads=H, kv_heads=G, dim=D, vdim=V, scale=0.4, q_temp={"coef": 0.8, "every": 16})
+    wf = {k: v.float() for k, v in w.items()}
+    want = [pb.mixer_attention(x, m, wf, "m.", 1e-6) for x in xs]
+    quiet = xs[0].clone()
+    quiet[3] /= 20.0
+    assert rel(pb.mixer_attention(quiet, m, wf, "m.", 1e-6)[600:], want[0][600:]) > 0.05       # the far key matters
+    no_temp = dict(m, q_temp=None)
+    assert rel(pb.mixer_attention(xs[0], no_temp, wf, "m.", 1e-6)[600:], want[0][600:]) > 0.01
+    got = run_in_cuts(MixerHarness(part, rt, hidden, page_size=16, n_pages=64, max_positions=1024), xs,
+                      CUTS["prompt then decode"])
+    for a, b in zip(got, want):
+        assert rel(a, b) < tol
+
+
+@pytest.mark.parametrize("cut", list(CUTS))
+@pytest.mark.parametrize("H,D,R,rot,V,C,window,q_rank,page", [
+    (4, 16, 32, 16, 16, 48, 21, None, 4), (3, 12, 6, 4, 20, 40, 1, None, 8), (2, 24, 8, 8, 28, 36, None, 20, 4),
+    (8, 64, 64, 64, 64, 192, 64, None, 64), (4, 32, 32, 32, 64, 128, 65, 96, 64), (2, 16, 16, 0, 16, 32, 40, None, 16)])
+@pytest.mark.parametrize("dtype", list(DTYPES))
+def test_latent_attention_alone_at_its_window_edges(dtype, H, D, R, rot, V, C, window, q_rank, page, cut):
+    """Both latent mixers, windows of one, of a page, of a page and one, none; a loud row at position 5 whose rotated
+    key part and latent stand out while it is inside the window: the plain implementation tells the positions just
+    inside from those just outside, and the engine agrees with it at all of them."""
+    dt, tol = DTYPES[dtype]
+    hidden = 64
+    spec = latent_spec(hidden, H, D, R, rot, V, C, 0.2, window=window, q_rank=q_rank)
+    w = random_tensors(spec, seed=H + C, std=0.25)
+    part, rt = load_part(spec, w, dt)
+    xs = inputs(hidden, (150, 37), 7, dt, loud=(0, 5))
+    m = dict(heads=H, dim=D, rot_dim=R, vdim=V, kv_rank=C, scale=0.2, rot={"dims": max(rot, 0), "base": 10000.0})
+    if window:
+        m["mask"] = {"size": window}
+    wf = {k: v.float() for k, v in w.items()}
+    plain = lambda x: pb.mixer_latent_attention(x, m, wf, "m.", 1e-6, query_latent=q_rank is not None, gated=q_rank is None)
+    want = [plain(x) for x in xs]
+    if window and window > 1:
+        quiet = xs[0].clone()
+        quiet[5] /= 20.0
+        other = plain(quiet)
+        inside, outside = 5 + window - 1, 5 + window
+        assert rel(other[inside], want[0][inside]) > 1e-3                      # the last position that sees row 5
+        assert float((other[outside:] - want[0][outside:]).abs().max()) == 0.0    # the first that does not
+    got = run_in_cuts(MixerHarness(part, rt, hidden, page_size=page, n_pages=256 // page + 8), xs, CUTS[cut])
+    for a, b in zip(got, want):
+        assert rel(a, b) < tol
+
+
+# ------------------------------------------------------------------ whole models
+def prompts_for(name, n=5, hi=150, seed=0):
+    cfg = CONFIGS[name][0]
+    rng = random.Random(seed)
+    lens = [1, 2, hi] + [rng.randint(3, hi) for _ in range(max(0, n - 3))]
+    return {f"r{i}": [rng.randrange(cfg["vocab"]) for _ in range(L)] for i, L in enumerate(lens)}
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    tmp = tmp_path_factory.mktemp("bobepel_models")
+    return {name: make_folder(tmp, name) for name in CONFIGS}
+
+
+@pytest.fixture(scope="module")
+def expected(folders):
+    import plain_qwen2moe as reader
+
+    out = {}
+    for name in CONFIGS:
+        cfg, w = reader.load_model(folders[name], torch.float32)
+        out[name] = (cfg, w, {rid: pb.forward(cfg, w, t) for rid, t in prompts_for(name).items()})
+    return out
+
+
+def engine(folder, dtype, **kw):
+    from ferrox_b200 import Engine
+
+    kw.setdefault("page_size", 64 if folder.endswith("_C") else 8)     # C: the page size of serving
+    kw.setdefault("n_pages", 64)
+    kw.setdefault("max_slots", 4)
+    return Engine.from_folder(folder, dtype=dtype, **kw)
+
+
+def router_is_clear(cfg, w, tokens, margin=0.02):
+    """Per position: whether, in every layer, the plain implementation separates the last chosen expert from the
+    next one by more than ``margin`` (a bfloat16 engine may rightly choose the other one where it does not)."""
+    eps = cfg["norm"]["eps"]
+    x = w["embed"][torch.as_tensor(tokens)].float()
+    clear = torch.ones(len(tokens), dtype=torch.bool)
+    for i, entry in enumerate(cfg["layers"]):
+        src = entry.get("weights_of", i)
+        f = entry.get("mlp")
+        if f is not None and f["router"]["top"] < f["router"]["experts"]:
+            h = pb.norm_one_plus(x, w[f"l{src}.norm1"], eps)
+            s = torch.sigmoid(h @ w[f"l{src}.mlp.router"].T).sort(dim=-1, descending=True).values
+            k = f["router"]["top"]
+            clear &= (s[:, k - 1] - s[:, k]) > margin
+        x = pb.layer(x, entry, w, src, eps)
+    return clear
+
+
+def compare(got, want, tol, what, clear=None):
+    if tol > 1e-3:
+        tol = 6e-2     # bfloat16 through several layers of a narrow model: every activation between kernels is rounded
+    n = ok = 0
+    for rid in want:
+        assert got[rid].shape == want[rid].shape, (what, rid)
+        assert torch.isfinite(got[rid]).all(), (what, rid)
+        rows = clear[rid] if clear is not None else torch.ones(want[rid].shape[0], dtype=torch.bool)
+        n += rows.numel()
+        ok += int(rows.sum())
+        if rows.any():
+            err = float((got[rid][rows] - want[rid][rows]).abs().max() / want[rid].abs().max())
+            assert err < tol, (what, rid, err)
+    assert ok >= 0.5 * n, (what, "too few positions with a clear choice of experts")
+
+
+RUNS = {
+    "whole": lambda eng, p: ru.run_whole(eng, p),
+    "decoded tail": lambda eng, p: ru.run_tail_decode(eng, p, tail=50),
+    "portions": lambda eng, p: ru.run_portions(eng, p),
+    "decoding together": lambda eng, p: ru.run_decode_together(eng, p, tail=9),
+    "mixed": lambda eng, p: ru.run_mixed(eng, p, seed=3, max_live=3),
+}
+
+
+def clear_rows(expected, name, dtype):
+    """bfloat16: a choice of experts within rounding of the next one excuses the position."""
+    if dtype != "bfloat16":
+        return None
+    cfg, w, _ = expected[name]
+    out = {}
+    for rid, toks in prompts_for(name).items():
+        out[rid] = router_is_clear(cfg, w, toks)
+    return out
+
+
+@pytest.mark.parametrize("run", list(RUNS))
+@pytest.mark.parametrize("name", sorted(CONFIGS))
+@pytest.mark.parametrize("dtype", list(DTYPES))
+def test_model_under_every_cut(folders, expected, dtype, name, run):
+    _, tol = DTYPES[dtype]
+    eng = engine(folders[name], dtype)
+    got = RUNS[run](eng, prompts_for(name))
+    compare(got, expected[name][2], tol, f"{name} {dtype} {run}", clear_rows(expected, name, dtype))
+    eng.cache.check_invariants()
+    assert all(n == eng.cache.groups[k].pool.n_pages for k, n in eng.cache.free_pages().items())   # all given back
+
+
+@pytest.mark.parametrize("name", sorted(CONFIGS))
+def test_cuts_agree_with_each_other_to_rounding(folders, name):
+    eng = engine(folders[name], "float32")
+    p = prompts_for(name)
+    whole, mixed = ru.run_whole(eng, p), ru.run_mixed(eng, p, seed=5, max_live=4)
+    for rid in p:
+        assert float((whole[rid] - mixed[rid]).abs().max() / whole[rid].abs().max()) < 2e-5
+
+
+def test_residual_stream_after_every_layer(folders, expected):
+    """Layer by layer in 32-bit: the model's blocks run one after the other on the plain implementation's stream."""
+    from ferrox_b200.engine.batch import StepEntry
+
+    cfg, w, _ = expected["A"]
+    toks = prompts_for("A")["r3"]
+    want_logits, after = pb.forward(cfg, w, toks, return_layers=True)
+    eng = engine(folders["A"], "float32")
+    seen = []
+    model = eng.model
+    for block in model.layers:
+        inner = block.forward
+
+        def spy(h, batch, cache, _inner=inner, **kw):
+            out = _inner(h, batch, cache, **kw)
+            seen.append(h.detach().clone().cpu())
+            return out
+        block.forward = spy
+    slot = eng.open_request()
+    got = eng.step([StepEntry(slot, toks, want=list(range(len(toks))))]).cpu()
+    assert len(seen) == len(cfg["layers"])
+    for i, h in enumerate(seen):
+        assert rel(h, after[i]) < 2e-5, i
+    assert rel(got, want_logits) < 5e-5
+
+
+@pytest.mark.parametrize("dtype", list(DTYPES))
+def test_long_decoding_past_every_window_with_pages_given_back(folders, dtype):
+    """Three tokens of prompt, then 300 decoded one by one; the windowed layers give their old pages back as they go
+    (their pool holds less than the request), the others keep all."""
+    import plain_qwen2moe as reader
+
+    _, tol = DTYPES[dtype]
+    cfg, w = reader.load_model(folders["A"], torch.float32)
+    rng = random.Random(9)
+    toks = [rng.randrange(cfg["vocab"]) for _ in range(303)]
+    want = pb.forward(cfg, w, toks)
+    eng = engine(folders["A"], dtype, page_size=8, n_pages={None: 40, 21: 6}, max_slots=2)   # 48 windowed positions
+    c = ru.Collector(eng)
+    c.step({"x": toks[:3]})
+    for t in toks[3:]:
+        c.step({"x": [t]})
+    compare({"x": c.stacked("x")}, {"x": want}, tol, "long decoding")
+    assert eng.cache.peak_pages[21] <= 6
+
+
+@pytest.mark.parametrize("name", sorted(CONFIGS))
+def test_greedy_generation_through_the_scheduler(folders, name):
+    import plain_qwen2moe as reader
+
+    cfg, w = reader.load_model(folders[name], torch.float32)
+    rng = random.Random(4)
+    prompts = [[rng.randrange(cfg["vocab"]) for _ in range(n)] for n in (5, 1, 23)]
+
+    def greedy(p, n):
+        toks = list(p)
+        for _ in range(n):
+            toks.append(int(pb.forward(cfg, w, toks)[-1].argmax()))
+        return toks[len(p):]
+
+    want = [greedy(p, 12) for p in prompts]
+    eng = engine(folders[name], "float32")
+    assert eng.graphs is not None            # every part of the model can be captured: decode steps replay graphs
+    got = eng.generate(prompts, max_new_tokens=12, max_batch_tokens=16)     # prompts go in portions
+    assert got == want
+    again = eng.generate(prompts[::-1], max_new_tokens=12)                  # slots and pages used again
+    assert again == want[::-1]
+    bf = engine(folders[name], "bfloat16").generate(prompts, max_new_tokens=12)
+    assert all(len(g) == 12 for g in bf)
+    for p, g in zip(prompts, bf):
+        logits = pb.forward(cfg, w, (p + g)[:-1])
+        close = sum(float(logits[len(p) - 1 + i].max() - logits[len(p) - 1 + i][tok]) <= 2 * 6e-2 * float(logits.abs().max())
+                    for i, tok in enumerate(g))
+        assert close >= 10      # (a choice of experts within rounding may differ at a position or two)
+
+
+def test_trace_replay_and_command_line_with_a_bobepel_folder(folders, tmp_path):
+    import json
+    import os
+    import subprocess
+    import sys
+
+    import numpy as np
+    import plain_qwen2moe as reader
+
+    cfg, w = reader.load_model(folders["B"], torch.float32)
+    toks = [3, 90, 7, 7, 45, 21, 9, 81]
+    want = pb.forward(cfg, w, toks)
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": toks[:5], "want": [0, 4]}], "end": []},
+        {"step": 1, "entries": [{"id": "a", "tokens": toks[5:6], "want": []}], "end": []},
+        {"step": 2, "entries": [{"id": "a", "tokens": toks[6:], "want": [1]}, {"id": "b", "tokens": toks[:2], "want": [1]}],
+         "end": ["a", "b"]},
+    ]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = tmp_path / "out"
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", folders["B"], "--dtype", "float32",
+                        "--out", str(out), "--max-tokens", "128"], input="\n".join(json.dumps(s) for s in steps) + "\n",
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [l for l in r.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2"]
+    s0 = torch.from_numpy(np.fromfile(out / "0.f32", dtype="<f4").reshape(2, -1))
+    s2 = torch.from_numpy(np.fromfile(out / "2.f32", dtype="<f4").reshape(2, -1))
+    assert rel(s0, want[[0, 4]]) < 5e-5 and rel(s2, want[[7, 1]]) < 5e-5
+    nxt = [int(pb.forward(cfg, w, toks[:4])[-1].argmax())]
+    nxt.append(int(pb.forward(cfg, w, toks[:4] + nxt)[-1].argmax()))
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "ferrox"), "-m", folders["B"], "--tokens", "3,90,7,7",
+                        "-n", "2", "--temp", "0", "--dtype", "float32", "--ignore-eos", "--repeat-penalty", "1.0"],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [int(t) for t in r.stdout.split()] == nxt
+
+
+def test_preemption_and_decoding_ahead(folders):
+    """A request that is preempted gives its pages and slot back and is recomputed; greedy decode steps are replayed
+    graphs issued one ahead of the host."""
+    import plain_qwen2moe as reader
+
+    cfg, w = reader.load_model(folders["B"], torch.float32)
+    prompts = [[i + 1, i + 3, i + 7, 90, 4, 8, 15, 16] for i in range(4)]
+
+    def greedy(p, n):
+        toks = list(p)
+        for _ in range(n):
+            toks.append(int(pb.forward(cfg, w, toks)[-1].argmax()))
+        return toks[len(p):]
+
+    want = [greedy(p, 20) for p in prompts]
+    small = engine(folders["B"], "float32", page_size=4, n_pages=14, max_slots=4)     # 4 x 28 positions do not fit 56
+    outs, stats = small.generate(prompts, max_new_tokens=20, return_stats=True)
+    assert stats["preemptions"] >= 1 and outs == want
+    small.cache.check_invariants()
+    roomy = engine(folders["B"], "float32", n_pages=64)
+    outs, stats = roomy.generate(prompts, max_new_tokens=20, return_stats=True)
+    assert outs == want and stats["ahead_steps"] >= 8 and stats["preemptions"] == 0
