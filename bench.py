@@ -3,6 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--shape a2.7b|a14b] [--repeats 3]
     python bench.py --designs        (the Safepel design beside the dense decoder at equal sizes; its own JSON line)
+    python bench.py --designs bobepel   (the Bobepel design beside the Qwen2-MoE decoder at equal sizes)
 
 Default workload: the layer sizes of the Qwen1.5-MoE-A2.7B shape (24 layers, hidden
 2048, 16 heads of 128, 60 experts top-4 of width 1408, shared expert 5632, vocab
@@ -184,8 +185,38 @@ def dense_like(width, layers, ff, vocab=32768):
                 tie_word_embeddings=False, max_position_embeddings=CONTEXT)
 
 
+def bobepel_shape(width, layers, vocab=32768, window=1024):
+    """Layer sizes that resemble a real model's: 16 heads of 128 at width 2,048 (a latent of 512 with 64 rotated
+    elements behind the latent layers), 60 experts of which a token uses 4, a shared expert four times as wide:
+    plain attention, two windowed latent layers and one whose queries pass a latent, in turn."""
+    h = width // 128
+    ff = width * 11 // 16 // 64 * 64
+    mlp = {"kind": "moe", "expert": {"ff": ff, "limit": 7.0}, "router": {"experts": 60, "top": 4},
+           "shared": {"ff": 4 * ff, "limit": 7.0}}
+    att = {"type": "attention", "mlp": mlp, "mixer": {
+        "heads": h, "kv_heads": max(1, h // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+        "q_temp": {"coef": 0.1, "every": 1024}}}
+    lat = {"type": "latent_attention", "mlp": mlp, "mixer": {
+        "heads": h, "dim": 128, "rot_dim": 64, "rot": {"dims": 64, "base": 1000000.0}, "vdim": 128, "kv_rank": 512,
+        "scale": 192 ** -0.5, "mask": {"size": window}}}
+    lat2 = {"type": "latent_attention_2", "mlp": mlp, "mixer": dict(lat["mixer"], q_rank=3 * width // 4)}
+    del lat2["mixer"]["mask"]
+    return {"architecture": "Bobepel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "max_positions": CONTEXT,
+            "layers": [(att, lat, lat, lat2)[i % 4] for i in range(layers)]}
+
+
+def moe_like(width, layers, vocab=32768):
+    """The closest existing model: the Qwen2-MoE decoder with the same width, layers, experts and expert widths,
+    16 heads of 128 on 4 key heads at width 2,048."""
+    h = width // 128
+    ff = width * 11 // 16 // 64 * 64
+    return dict(A27B, num_hidden_layers=layers, hidden_size=width, num_attention_heads=h, num_key_value_heads=max(1, h // 4),
+                moe_intermediate_size=ff, shared_expert_intermediate_size=4 * ff, intermediate_size=4 * ff,
+                vocab_size=vocab, max_position_embeddings=CONTEXT)
+
+
 def compare_designs(args) -> int:
-    """Prefill and decode throughput of the Safepel design and of the dense decoder at a few equal sizes (random
+    """Prefill and decode throughput of a design and of the closest existing decoder at a few equal sizes (random
     bfloat16 weights), with the device time of every class of kernel from a traced pass beside them."""
     import torch
 
@@ -197,6 +228,8 @@ def compare_designs(args) -> int:
     sizes = [(1024, 8, 2816), (2048, 8, 5632), (4096, 4, 11264)]
     if args.layers:
         sizes = [(w, args.layers, ff) for w, _, ff in sizes]
+    if getattr(args, "widths", ""):
+        sizes = [s for s in sizes if str(s[0]) in args.widths.split(",")]
 
     def timed(fn):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -281,6 +314,15 @@ def compare_designs(args) -> int:
 
     pk = peaks()
     rows = []
+    if args.designs == "bobepel":
+        for width, layers, _ in sizes:
+            a, b = bobepel_shape(width, layers), moe_like(width, layers)
+            rows.append({"width": width, "layers": layers, "expert_ff": b["moe_intermediate_size"],
+                         "bobepel": measure(a), "qwen2_moe": measure(b)})
+        print(json.dumps({"designs": "Bobepel beside the Qwen2-MoE decoder at equal size", "dtype": "bf16", "batch": batch,
+                          "prompt_tokens": PREFILL_TOKENS, "decode_steps_timed": steps, "peaks": pk,
+                          "data": "synthetic: random N(0,0.02) weights, uniform random token ids", "sizes": rows}))
+        return 0
     for width, layers, ff in sizes:
         a, b = safepel_shape(width, layers, ff), dense_like(width, layers, ff)
         rows.append({"width": width, "layers": layers, "ff": ff, "dense_ff": b["intermediate_size"],
@@ -304,9 +346,11 @@ def main() -> int:
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--page-size", type=int, default=64)
     ap.add_argument("--repeats", type=int, default=3, help="timed regions of --steps steps each; the median counts")
-    ap.add_argument("--designs", action="store_true",
-                    help="instead of the default workload: prefill and decode of the Safepel design beside the dense "
-                         "Qwen2 decoder at a few equal sizes, with device time per class of kernel")
+    ap.add_argument("--designs", nargs="?", const="safepel", default=None, choices=["safepel", "bobepel"],
+                    help="instead of the default workload: prefill and decode of a design beside the closest existing "
+                         "decoder at a few equal sizes, with device time per class of kernel (safepel: beside the dense "
+                         "Qwen2 decoder; bobepel: beside the Qwen2-MoE decoder)")
+    ap.add_argument("--widths", default="", help="--designs: only these widths (commas), e.g. 2048")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
