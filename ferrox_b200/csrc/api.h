@@ -55,7 +55,7 @@ int fx_general_attention(const void* q, long ldq, long ldqh, const void* k_pages
                          const int* block_table, int table_width, int page_size, const int* positions,
                          const int* token_seq, const int* seq_slot, const int* items, int n_items, void* out, long ldo,
                          long ldoh, int n_heads, int n_kv_heads, int key_dim, int value_dim, int window, float scale,
-                         const float* slopes, void* stream);
+                         const float* slopes, int n_splits, float* part_o, float* part_ml, void* stream);
 
 int fx_prefill_attention_tc(const void* q, long ldq, int n_tokens, const void* k_pages, const void* v_pages, int n_pages,
                             const int* block_table, int table_width, int page_size, const int* items, int n_items,

@@ -16,6 +16,9 @@
 // Work items: `items` int32 [n, 5] = (first flat token, tokens, entry, first query head, heads) from the host for
 // prompt portions; items == nullptr: one token a tile, grid = (tokens, kv heads x head chunks), the entry from
 // token_seq, so that a captured decode step replays unchanged.  Positions are read from `positions` either way.
+// In that form a token's visible keys may be cut into n_splits runs (fx_split_range: equal runs, whatever the
+// context length), one block each, so that a step of few tokens fills the machine; a block then leaves its
+// unnormalised sums and its (maximum, sum) in scratch and a second kernel adds a row's runs up.
 #include "common.cuh"
 #include "api.h"
 
@@ -59,6 +62,9 @@ struct GArgs {
     const float* slopes;
     int alias;        // the values are the leading columns of the key rows: one copy in shared memory serves both
     int part_cols;    // value columns a set of 4 warps takes (a multiple of 16)
+    int n_splits;     // > 1 (only without items): blockIdx.z takes one run of the token's keys
+    float* part_o;    // [tokens][heads][n_splits][value_dim] unnormalised sums, relative to the run's maximum
+    float* part_ml;   // [tokens][heads][n_splits][2] the run's maximum (in units of log2 e) and its sum
 };
 
 // DVMAX: most value columns one warp accumulates.  NSPLIT: sets of 4 warps that share out the value columns.
@@ -96,8 +102,14 @@ __global__ void __launch_bounds__(128 * NSPLIT) general_attention_kernel(GArgs a
     const int rows = n_tok * n_h;
     const int* table = a.block_table + (long)a.seq_slot[entry] * a.table_width;
     const int kchunks = a.key_dim / 8, vchunks = a.value_dim / 8;   // 16-byte chunks per row
-    const int last_pos = pos0 + n_tok - 1;
-    const int key_lo = (a.window > 0 && pos0 - a.window + 1 > 0) ? pos0 - a.window + 1 : 0;   // first key any row may see
+    int last_pos = pos0 + n_tok - 1;
+    int key_lo = (a.window > 0 && pos0 - a.window + 1 > 0) ? pos0 - a.window + 1 : 0;   // first key any row may see
+    if (a.n_splits > 1) {      // (one token a tile) this block's run of the token's keys
+        int k_begin, k_end;
+        fx_split_range(pos0, key_lo, blockIdx.z, a.n_splits, 0, k_begin, k_end);
+        if (k_begin >= k_end) return;      // nothing of this run is visible: the merge skips it by the same rule
+        key_lo = k_begin; last_pos = k_end - 1;
+    }
     const int kb_begin = (key_lo / BKEY) * BKEY;
     const int n_blocks = (last_pos - kb_begin) / BKEY + 1;
 
@@ -145,15 +157,16 @@ __global__ void __launch_bounds__(128 * NSPLIT) general_attention_kernel(GArgs a
     const int r0 = qrow0 + g, r1 = r0 + 8;
     // each row's own position, first visible key and slope (in units of log2 e)
     const int p_row0 = pos0 + min(r0, rows - 1) / n_h, p_row1 = pos0 + min(r1, rows - 1) / n_h;
-    const int lo0 = a.window > 0 ? p_row0 - a.window + 1 : 0, lo1 = a.window > 0 ? p_row1 - a.window + 1 : 0;
+    const int lo0 = max(a.window > 0 ? p_row0 - a.window + 1 : 0, key_lo), lo1 = max(a.window > 0 ? p_row1 - a.window + 1 : 0, key_lo);
+    const int hi0 = min(p_row0, last_pos), hi1 = min(p_row1, last_pos);      // each row's last visible key here
     float sl0 = 0.f, sl1 = 0.f;
     if (a.slopes) {
         sl0 = a.slopes[head0 + min(r0, rows - 1) % n_h] * 1.4426950408889634f;
         sl1 = a.slopes[head0 + min(r1, rows - 1) % n_h] * 1.4426950408889634f;
     }
     // the warp's rows cover the tokens of rows qrow0 .. qrow0 + 15
-    const int w_first = pos0 + min(qrow0, rows - 1) / n_h, w_last = pos0 + min(qrow0 + 15, rows - 1) / n_h;
-    const int w_lo = (a.window > 0 && w_first - a.window + 1 > 0) ? w_first - a.window + 1 : 0;
+    const int w_first = pos0 + min(qrow0, rows - 1) / n_h, w_last = min(last_pos, pos0 + min(qrow0 + 15, rows - 1) / n_h);
+    const int w_lo = max(key_lo, (a.window > 0 && w_first - a.window + 1 > 0) ? w_first - a.window + 1 : 0);
 
     for (int blk = 0; blk < n_blocks; ++blk) {
         const int buf = blk & 1;
@@ -189,9 +202,9 @@ __global__ void __launch_bounds__(128 * NSPLIT) general_attention_kernel(GArgs a
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const int key = kb + j * 8 + 2 * t4 + e;
-                    s[j][e] = (key > p_row0 || key < lo0) ? -INFINITY
+                    s[j][e] = (key > hi0 || key < lo0) ? -INFINITY
                                                           : fmaf(-sl0, (float)(p_row0 - key), s[j][e] * a.scale_log2e);
-                    s[j][2 + e] = (key > p_row1 || key < lo1) ? -INFINITY
+                    s[j][2 + e] = (key > hi1 || key < lo1) ? -INFINITY
                                                               : fmaf(-sl1, (float)(p_row1 - key), s[j][2 + e] * a.scale_log2e);
                     mx0 = fmaxf(mx0, s[j][e]);
                     mx1 = fmaxf(mx1, s[j][2 + e]);
@@ -240,6 +253,24 @@ __global__ void __launch_bounds__(128 * NSPLIT) general_attention_kernel(GArgs a
     }
     cp_wait<0>();
 
+    if (a.n_splits > 1) {
+        // ---- this run's sums as they are, for the merge ------------------------------
+        const long row0 = ((long)tok0 * a.n_heads + head0 + min(r0, rows - 1)) * a.n_splits + blockIdx.z;
+        const long row1 = ((long)tok0 * a.n_heads + head0 + min(r1, rows - 1)) * a.n_splits + blockIdx.z;
+        if (part == 0 && t4 == 0 && qrow0 < rows) {
+            if (r0 < rows) { a.part_ml[row0 * 2] = m0; a.part_ml[row0 * 2 + 1] = l0; }
+            if (r1 < rows) { a.part_ml[row1 * 2] = m1; a.part_ml[row1 * 2 + 1] = l1; }
+        }
+#pragma unroll
+        for (int i = 0; i < ON; ++i) {
+            const int col = i * 8 + 2 * t4;
+            if (col < my_cols) {
+                if (r0 < rows) *reinterpret_cast<float2*>(a.part_o + row0 * a.value_dim + col0 + col) = make_float2(o[i][0], o[i][1]);
+                if (r1 < rows) *reinterpret_cast<float2*>(a.part_o + row1 * a.value_dim + col0 + col) = make_float2(o[i][2], o[i][3]);
+            }
+        }
+        return;
+    }
     // ---- normalise and store ---------------------------------------------------------
     const float inv0 = l0 > 0.f ? 1.f / l0 : 0.f, inv1 = l1 > 0.f ? 1.f / l1 : 0.f;
     bf16* o0 = a.out + (long)(tok0 + min(r0, rows - 1) / n_h) * a.ldo + (long)(head0 + min(r0, rows - 1) % n_h) * a.ldoh + col0;
@@ -254,6 +285,34 @@ __global__ void __launch_bounds__(128 * NSPLIT) general_attention_kernel(GArgs a
     }
 }
 
+// One block a (token, head): the runs of a token's keys added up, each weighted by 2^(its maximum - the largest).
+__global__ void general_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                     const int* __restrict__ positions, bf16* __restrict__ out, long ldo, long ldoh,
+                                     int n_heads, int value_dim, int n_splits, int window)
+{
+    fx_pdl_wait();
+    const int tkn = blockIdx.x, h = blockIdx.y;
+    const long base = ((long)tkn * n_heads + h) * n_splits;
+    const int pos = positions[tkn];
+    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    auto has_keys = [&](int s) { int b, e; fx_split_range(pos, lo, s, n_splits, 0, b, e); return b < e; };
+    float mm = -INFINITY;
+    for (int s = 0; s < n_splits; ++s)
+        if (has_keys(s)) mm = fmaxf(mm, part_ml[(base + s) * 2]);
+    for (int e = threadIdx.x; e < value_dim; e += blockDim.x) {
+        float ll = 0.f, acc = 0.f;
+        for (int s = 0; s < n_splits; ++s) {
+            if (!has_keys(s)) continue;
+            const float ms = part_ml[(base + s) * 2];
+            if (ms == -INFINITY) continue;
+            const float w = exp2f(ms - mm);
+            ll += part_ml[(base + s) * 2 + 1] * w;
+            acc += part_o[(base + s) * value_dim + e] * w;
+        }
+        out[(long)tkn * ldo + (long)h * ldoh + e] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+    }
+}
+
 template <int DVMAX, int NSPLIT>
 int launch(dim3 grid, size_t smem, cudaStream_t s, const GArgs& a)
 {
@@ -263,17 +322,24 @@ int launch(dim3 grid, size_t smem, cudaStream_t s, const GArgs& a)
         if (e != cudaSuccess) return (int)e;
     }
     fx_launch_pdl(kern, grid, dim3(128 * NSPLIT), smem, s, a);
+    if (a.n_splits > 1)
+        fx_launch_pdl(general_merge_kernel, dim3(grid.x, a.n_heads), dim3(64), 0, s, (const float*)a.part_o,
+                      (const float*)a.part_ml, a.positions, a.out, a.ldo, a.ldoh, a.n_heads, a.value_dim, a.n_splits,
+                      a.window);
     return fx_launch_status();
 }
 
 }  // namespace
 
-// Whether fx_general_attention takes these sizes (the caller goes to fx_paged_attention_ex otherwise).
+// Whether fx_general_attention takes these sizes (the caller goes to fx_paged_attention_ex otherwise): 0, or how
+// many of its blocks an SM holds.
 extern "C" int fx_general_attention_ok(int key_dim, int value_dim, int alias)
 {
     if (key_dim <= 0 || value_dim <= 0 || key_dim % 16 || value_dim % 16 || key_dim > 640 || value_dim > 512) return 0;
     const size_t smem = (size_t)(BQ + 2 * BKEY) * (key_dim * 2 + 16) + (alias ? 0 : (size_t)2 * BKEY * (value_dim * 2 + 16));
-    return smem <= 220 * 1024;
+    if (smem > 220 * 1024) return 0;
+    const int fit = (int)((227 * 1024) / (smem + 1024));
+    return fit > 4 ? 4 : fit;
 }
 
 // items: int32 [n_items, 5] = (first flat token, tokens, entry, first query head, heads), heads of one kv head,
@@ -283,7 +349,7 @@ extern "C" int fx_general_attention(const void* q, long ldq, long ldqh, const vo
                                     const int* positions, const int* token_seq, const int* seq_slot, const int* items,
                                     int n_items, void* out, long ldo, long ldoh, int n_heads, int n_kv_heads,
                                     int key_dim, int value_dim, int window, float scale, const float* slopes,
-                                    void* stream)
+                                    int n_splits, float* part_o, float* part_ml, void* stream)
 {
     if (n_items <= 0) return FX_OK;
     if (n_kv_heads <= 0 || n_heads % n_kv_heads) return FX_ERR_SIZE;
@@ -300,9 +366,11 @@ extern "C" int fx_general_attention(const void* q, long ldq, long ldqh, const vo
     a.out = (bf16*)out; a.ldo = ldo; a.ldoh = ldoh;
     a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.key_dim = key_dim; a.value_dim = value_dim; a.window = window;
     a.scale_log2e = scale * 1.4426950408889634f; a.slopes = slopes; a.alias = alias;
+    a.n_splits = n_splits > 1 ? n_splits : 1; a.part_o = part_o; a.part_ml = part_ml;
+    if (a.n_splits > 1 && (items || !part_o || !part_ml || a.n_splits > 65535)) return FX_ERR_SIZE;
     const size_t smem = (size_t)(BQ + 2 * BKEY) * (key_dim * 2 + 16) + (alias ? 0 : (size_t)2 * BKEY * (value_dim * 2 + 16));
     const int group = n_heads / n_kv_heads;
-    dim3 grid = items ? dim3(n_items) : dim3(n_items, n_kv_heads * ((group + BQ - 1) / BQ));
+    dim3 grid = items ? dim3(n_items) : dim3(n_items, n_kv_heads * ((group + BQ - 1) / BQ), a.n_splits);
     cudaStream_t s = (cudaStream_t)stream;
     if (value_dim <= 64) { a.part_cols = 64; return launch<64, 1>(grid, smem, s, a); }
     if (value_dim <= 128) { a.part_cols = 128; return launch<128, 1>(grid, smem, s, a); }

@@ -51,7 +51,7 @@ _SIGNATURES = {
                               _F, _P, _P],
     "fx_general_attention_ok": [_I, _I, _I],
     "fx_general_attention": [_P, _L, _L, _P, _P, _L, _L, _P, _I, _I, _P, _P, _P, _P, _I, _P, _L, _L, _I, _I, _I, _I, _I, _F,
-                             _P, _P],
+                             _P, _I, _P, _P, _P],
     "fx_qk_norm_store": [_P, _I, _L, _P, _P, _P, _P, _P, _I, _F, _F, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "fx_latent_prep": [_P, _L, _P, _L, _I, _P, _P, _P, _P, _I, _F, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P,
                        _P],
@@ -530,13 +530,14 @@ def paged_attention_ex(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, block_table, pa
 GENERAL_TILE_ROWS = 64     # (token, head) pairs a tile of the tensor-core kernel of the general form holds
 
 
-def general_attention_ok(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, out, ldo, ldoh, key_dim, value_dim) -> bool:
-    """Whether :func:`general_attention` takes these operands (bfloat16, widths in steps of 16, 16-byte rows)."""
+def general_attention_ok(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, out, ldo, ldoh, key_dim, value_dim) -> int:
+    """Whether :func:`general_attention` takes these operands (bfloat16, widths in steps of 16, 16-byte rows): 0, or
+    how many of its blocks an SM holds."""
     alias = int(v_pages.data_ptr() == k_pages.data_ptr() and ldv == ldk and value_dim <= key_dim)
-    return (q.dtype == torch.bfloat16 and k_pages.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+    return int(q.dtype == torch.bfloat16 and k_pages.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
             and ldq % 8 == 0 and ldqh % 8 == 0 and ldk % 8 == 0 and ldv % 8 == 0 and ldo % 2 == 0 and ldoh % 2 == 0
             and q.data_ptr() % 16 == 0 and k_pages.data_ptr() % 16 == 0 and v_pages.data_ptr() % 16 == 0
-            and out.data_ptr() % 4 == 0 and bool(_get("fx_general_attention_ok")(key_dim, value_dim, alias)))
+            and out.data_ptr() % 4 == 0 and _get("fx_general_attention_ok")(key_dim, value_dim, alias))
 
 
 def general_attention_items(entries, n_heads: int, n_kv_heads: int):
@@ -562,15 +563,21 @@ def general_attention_items(entries, n_heads: int, n_kv_heads: int):
 
 def general_attention(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, block_table, page_size, positions, token_seq, seq_slot,
                       items, out, ldo, ldoh, n_heads, n_kv_heads, key_dim, value_dim, window, scale, slopes=None,
-                      stream=None):
+                      stream=None, n_splits=1, part_o=None, part_ml=None):
     """:func:`paged_attention_ex` in bfloat16 on the tensor cores (see :func:`general_attention_ok`).  ``items``: the
     device copy of :func:`general_attention_items`, or None when every entry brings one token (a tile a token and
-    kv head; nothing comes from the host, so a captured step replays unchanged)."""
+    kv head; nothing comes from the host, so a captured step replays unchanged).  ``n_splits`` > 1 (without items):
+    every token's visible keys are cut into that many runs, a block each; ``part_o`` float32 [T, heads, n_splits,
+    value_dim] and ``part_ml`` float32 [T, heads, n_splits, 2] are scratch, and a second kernel adds the runs up."""
+    global _launches
     n = items.shape[0] if items is not None else positions.numel()
+    if n_splits > 1:
+        _launches += 1
     call("fx_general_attention", _ptr(q), int(ldq), int(ldqh), _ptr(k_pages), _ptr(v_pages), int(ldk), int(ldv),
          _ptr(block_table), block_table.shape[1], page_size, _ptr(positions), _ptr(token_seq), _ptr(seq_slot),
          _ptr(items), n, _ptr(out), int(ldo), int(ldoh), n_heads, n_kv_heads, key_dim, value_dim, int(window or 0),
-         float(scale), _ptr(slopes), stream if stream is not None else stream_ptr())
+         float(scale), _ptr(slopes), int(n_splits), _ptr(part_o), _ptr(part_ml),
+         stream if stream is not None else stream_ptr())
     return out
 
 

@@ -270,8 +270,21 @@ def general_attention(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, out, ldo, ldoh, 
     """Attention over pages in its general form (keys and values of different widths, strided queries and outputs, an
     optional distance bias), by the kernel that fits the step: tiles of (token, head) pairs on the tensor cores
     in bfloat16, a warp per (token, head) on the CUDA cores in 32-bit and for widths that are no multiple of 16."""
-    if ops.general_attention_ok(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, out, ldo, ldoh, key_dim, value_dim):
-        items = None
+    per_sm = ops.general_attention_ok(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, out, ldo, ldoh, key_dim, value_dim)
+    if per_sm:
+        items, n_splits, part_o, part_ml = None, 1, None, None
+        if batch.max_new == 1:
+            # one token a request: cut every token's keys into runs, so that few tokens fill the machine (the number
+            # of runs is a function of the step's size and the context limit only: a captured step keeps its grid)
+            T = batch.n_tokens
+            tiles = n_kv_heads * -(-(n_heads // n_kv_heads) // ops.GENERAL_TILE_ROWS)
+            reach = cache.block_table.shape[1] * cache.page_size
+            if window is not None:
+                reach = min(reach, (window + 63) // 64 * 64 + 64)
+            _, n_splits = ops.decode_split_plan(T, tiles, reach, per_sm, single_is_final=True)
+            if n_splits > 1:
+                part_o = rt.empty(T, n_heads, n_splits, value_dim, dtype=torch.float32)
+                part_ml = rt.empty(T, n_heads, n_splits, 2, dtype=torch.float32)
         if batch.max_new > 1:
             key = ("general attention items", n_heads, n_kv_heads)
             items = batch.shared.get(key)
@@ -281,7 +294,8 @@ def general_attention(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, out, ldo, ldoh, 
                 batch.shared[key] = items
         return ops.general_attention(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, cache.block_table, cache.page_size,
                                      batch.positions, batch.token_seq, batch.seq_slot, items, out, ldo, ldoh, n_heads,
-                                     n_kv_heads, key_dim, value_dim, window, scale, slopes=slopes, stream=batch.stream)
+                                     n_kv_heads, key_dim, value_dim, window, scale, slopes=slopes, stream=batch.stream,
+                                     n_splits=n_splits, part_o=part_o, part_ml=part_ml)
     ops.paged_attention_ex(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, cache.block_table, cache.page_size, batch.positions,
                            batch.token_seq, batch.seq_slot, out, ldo, ldoh, n_heads, n_kv_heads, key_dim, value_dim,
                            window, scale, slopes=slopes, stream=batch.stream)
