@@ -55,6 +55,8 @@ class LayerCache:
     writes: bool = True
     window: Optional[int] = None
     states: Optional[Dict[str, torch.Tensor]] = None  # a state made of named tensors, each [max_slots, *shape]
+    table_host: Optional[np.ndarray] = None  # the host's view of the block table (int32 [max_slots, table_width]), for
+    #                                          mixers that plan a prompt step's work from the pages it reads
 
     @property
     def k(self) -> Optional[torch.Tensor]:
@@ -296,6 +298,7 @@ class CacheManager:
             writes=writes,
             window=g.window if g is not None else None,
             states=self._named_state[cache_index],
+            table_host=g.table if g is not None else None,
         )
 
     def kv_bytes(self) -> int:

@@ -52,7 +52,7 @@ int fx_paged_attention_ex(const void* q, long ldq, long ldqh, const void* k_page
 // token, tokens, entry, first query head, heads) or nullptr (one token a tile, n_items = tokens)
 int fx_general_attention_ok(int key_dim, int value_dim, int alias);
 int fx_general_attention(const void* q, long ldq, long ldqh, const void* k_pages, const void* v_pages, long ldk, long ldv,
-                         const int* block_table, int table_width, int page_size, const int* positions,
+                         const long* kv_strides, const int* block_table, int table_width, int page_size, const int* positions,
                          const int* token_seq, const int* seq_slot, const int* items, int n_items, void* out, long ldo,
                          long ldoh, int n_heads, int n_kv_heads, int key_dim, int value_dim, int window, float scale,
                          const float* slopes, int n_splits, float* part_o, float* part_ml, void* stream);
@@ -146,15 +146,15 @@ int fx_qk_norm_store(void* qkv, int dtype, long ld, const int* positions, const 
                      const void* wq, const void* wk, int w_dtype, float eps, float temp_coef, int temp_every, void* k_pages,
                      void* v_pages, const int* block_table, int table_width, int page_size, int n_tokens, int n_heads,
                      int n_kv_heads, int key_dim, int value_dim, int write_cache, int* status, void* stream);
-int fx_latent_prep(const void* q, long ldq, const void* dkv, long ld_dkv, int dtype, const int* positions,
+int fx_latent_prep(void* q, long ldq, const void* dkv, long ld_dkv, int dtype, const int* positions,
                    const int* token_seq, const int* seq_slot, const void* wc, int w_dtype, float eps, const float* cos_sin,
                    int rot_dims, void* q_plain, void* q_full, void* pages, const int* block_table, int table_width,
                    int page_size, int n_tokens, int n_heads, int plain_dim, int rot_dim, int rank, int write_cache,
-                   int* status, void* stream);
+                   int* status, void* stream);   // q_plain == nullptr: q's rotated parts are turned where they lie
 int fx_rmsnorm_rows(const void* x, int x_dtype, long ldx, const void* w, int w_dtype, float eps, void* out, int out_dtype,
                     long ldo, int n_rows, int n, void* stream);
-int fx_heads_to_tokens(const void* in, const void* gate, long ldg, void* out, long ldo, int dtype, int n_tokens,
-                       int n_heads, int width, void* stream);
+int fx_heads_to_tokens(const void* in, long in_ldt, long in_ldh, const void* gate, long ldg, void* out, long ldo, int dtype,
+                       int n_tokens, int n_heads, int width, void* stream);
 
 // softcap c > 0 (fx_paged_attention, fx_prefill_attention, fx_decode_attention): the scaled scores pass through
 // c * tanh(s / c) before the softmax; 0: none.  The kernels that stream pages by TMA take no cap: fx_decode_attention

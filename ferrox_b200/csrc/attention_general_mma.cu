@@ -53,6 +53,8 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
 struct GArgs {
     const bf16* q; long ldq, ldqh;
     const bf16* k_pages; const bf16* v_pages; long ldk, ldv;
+    long k_page_stride, k_head_stride, v_page_stride, v_head_stride;   // element (page, kv head, position, d) lies at
+                                                                       // page * page_stride + head * head_stride + position * ld + d
     const int* block_table; int table_width, page_size;
     const int* positions; const int* token_seq; const int* seq_slot;
     const int* items;
@@ -128,8 +130,8 @@ __global__ void __launch_bounds__(128 * NSPLIT) general_attention_kernel(GArgs a
             int page = -1;
             if (key <= last_pos && key >= key_lo) page = table[key / a.page_size];
             const bool ok = page >= 0;
-            const long place = ok ? ((long)page * a.n_kv_heads + kvh) * a.page_size + (key % a.page_size) : 0;
-            cp_async16(k_u + (buf * BKEY + r) * pk + ch * 16, a.k_pages + place * a.ldk + ch * 8, ok ? 16 : 0);
+            const long at = ok ? (long)page * a.k_page_stride + (long)kvh * a.k_head_stride + (long)(key % a.page_size) * a.ldk : 0;
+            cp_async16(k_u + (buf * BKEY + r) * pk + ch * 16, a.k_pages + at + ch * 8, ok ? 16 : 0);
         }
         if (a.alias) return;
         for (int c = threadIdx.x; c < BKEY * vchunks; c += NTHREADS) {
@@ -138,8 +140,8 @@ __global__ void __launch_bounds__(128 * NSPLIT) general_attention_kernel(GArgs a
             int page = -1;
             if (key <= last_pos && key >= key_lo) page = table[key / a.page_size];
             const bool ok = page >= 0;
-            const long place = ok ? ((long)page * a.n_kv_heads + kvh) * a.page_size + (key % a.page_size) : 0;
-            cp_async16(v_u + (buf * BKEY + r) * pv + ch * 16, a.v_pages + place * a.ldv + ch * 8, ok ? 16 : 0);
+            const long at = ok ? (long)page * a.v_page_stride + (long)kvh * a.v_head_stride + (long)(key % a.page_size) * a.ldv : 0;
+            cp_async16(v_u + (buf * BKEY + r) * pv + ch * 16, a.v_pages + at + ch * 8, ok ? 16 : 0);
         }
     };
     load_kv(0, 0);
@@ -344,8 +346,10 @@ extern "C" int fx_general_attention_ok(int key_dim, int value_dim, int alias)
 
 // items: int32 [n_items, 5] = (first flat token, tokens, entry, first query head, heads), heads of one kv head,
 // tokens x heads <= 64; or nullptr: one token a tile, n_items = tokens.  bfloat16 only.
+// kv_strides: nullptr for pages laid out [page][kv head][position][ld]; else (k page stride, k head stride, v page
+// stride, v head stride) in elements, for keys and values that lie otherwise (rows of all heads side by side).
 extern "C" int fx_general_attention(const void* q, long ldq, long ldqh, const void* k_pages, const void* v_pages, long ldk,
-                                    long ldv, const int* block_table, int table_width, int page_size,
+                                    long ldv, const long* kv_strides, const int* block_table, int table_width, int page_size,
                                     const int* positions, const int* token_seq, const int* seq_slot, const int* items,
                                     int n_items, void* out, long ldo, long ldoh, int n_heads, int n_kv_heads,
                                     int key_dim, int value_dim, int window, float scale, const float* slopes,
@@ -353,14 +357,18 @@ extern "C" int fx_general_attention(const void* q, long ldq, long ldqh, const vo
 {
     if (n_items <= 0) return FX_OK;
     if (n_kv_heads <= 0 || n_heads % n_kv_heads) return FX_ERR_SIZE;
-    const int alias = v_pages == k_pages && ldv == ldk && value_dim <= key_dim;
+    const long kps = kv_strides ? kv_strides[0] : (long)n_kv_heads * page_size * ldk, khs = kv_strides ? kv_strides[1] : (long)page_size * ldk;
+    const long vps = kv_strides ? kv_strides[2] : (long)n_kv_heads * page_size * ldv, vhs = kv_strides ? kv_strides[3] : (long)page_size * ldv;
+    const int alias = v_pages == k_pages && ldv == ldk && kps == vps && khs == vhs && value_dim <= key_dim;
     if (!fx_general_attention_ok(key_dim, value_dim, alias)) return FX_ERR_SIZE;
+    if (kps % 8 || khs % 8 || vps % 8 || vhs % 8) return FX_ERR_ALIGN;
     if (ldq % 8 || ldqh % 8 || ldk % 8 || ldv % 8 || ldo % 2 || ldoh % 2 || (uintptr_t)q % 16 || (uintptr_t)k_pages % 16 ||
         (uintptr_t)v_pages % 16 || (uintptr_t)out % 4)
         return FX_ERR_ALIGN;
     GArgs a;
     a.q = (const bf16*)q; a.ldq = ldq; a.ldqh = ldqh;
     a.k_pages = (const bf16*)k_pages; a.v_pages = (const bf16*)v_pages; a.ldk = ldk; a.ldv = ldv;
+    a.k_page_stride = kps; a.k_head_stride = khs; a.v_page_stride = vps; a.v_head_stride = vhs;
     a.block_table = block_table; a.table_width = table_width; a.page_size = page_size;
     a.positions = positions; a.token_seq = token_seq; a.seq_slot = seq_slot; a.items = items;
     a.out = (bf16*)out; a.ldo = ldo; a.ldoh = ldoh;

@@ -72,9 +72,11 @@ __global__ void qk_norm_store_kernel(T* __restrict__ qkv, long ld, const int* __
 //   q's R part of every head, turned the same way               -> q_full[head][token][C:C+R]
 // q_full's first C columns are filled afterwards by the product of q_plain with the keys' read-out matrix, so that a
 // score is one dot product of C + R elements against a cached row.  cos_sin: [tokens][rot_dims / 2][2].
+// q_plain == nullptr: the queries stay token rows and only their rotated parts are turned, in place (the form in
+// which keys and values are read out of the latent before the attention).
 // One block a token.
 template <typename T>
-__global__ void latent_prep_kernel(const T* __restrict__ q, long ldq, const T* __restrict__ dkv, long ld_dkv,
+__global__ void latent_prep_kernel(T* __restrict__ q, long ldq, const T* __restrict__ dkv, long ld_dkv,
                                    const int* __restrict__ positions, const int* __restrict__ token_seq,
                                    const int* __restrict__ seq_slot, const void* __restrict__ wc, int w_dtype, float eps,
                                    const float* __restrict__ cos_sin, int rot_dims, T* __restrict__ q_plain,
@@ -97,15 +99,16 @@ __global__ void latent_prep_kernel(const T* __restrict__ q, long ldq, const T* _
         else dst = pages + ((long)page * page_size + (pos % page_size)) * W;
     }
     // queries: the plain part head by head, the rotated part into its place behind the latent columns
-    const T* qr = q + (long)t * ldq;
-    for (int idx = threadIdx.x; idx < H * D; idx += blockDim.x) {
-        const int h = idx / D, i = idx - h * D;
-        q_plain[((long)h * n_tokens + t) * D + i] = qr[(long)h * (D + R) + i];
-    }
+    T* qr = q + (long)t * ldq;
+    if (q_plain)
+        for (int idx = threadIdx.x; idx < H * D; idx += blockDim.x) {
+            const int h = idx / D, i = idx - h * D;
+            q_plain[((long)h * n_tokens + t) * D + i] = qr[(long)h * (D + R) + i];
+        }
     for (int idx = threadIdx.x; idx < H * (R - half); idx += blockDim.x) {
         const int h = idx / (R - half), i = idx - h * (R - half);
-        const T* x = qr + (long)h * (D + R) + D;
-        T* o = q_full + ((long)h * n_tokens + t) * W + C;
+        T* x = qr + (long)h * (D + R) + D;
+        T* o = q_plain ? q_full + ((long)h * n_tokens + t) * W + C : x;   // no head-by-head copy: turned where it lies
         if (i < half) {
             const float a = to_f32(x[2 * i]), b = to_f32(x[2 * i + 1]), c = cs[2 * i], s = cs[2 * i + 1];
             o[2 * i] = from_f32<T>(a * c - b * s);
@@ -149,10 +152,11 @@ __global__ void rmsnorm_rows_kernel(const TI* __restrict__ x, long ldx, const vo
     for (int i = threadIdx.x; i < n; i += blockDim.x) o[i] = from_f32<TO>(to_f32(xr[i]) / r * load_any(w, w_dtype, i));
 }
 
-// out[t][h * V + v] = in[h][t][v] * (gate ? sigmoid(gate[t][h * V + v]) : 1): rows laid out head by head back into
-// token rows, with the output gate of the mixer applied on the way.
+// out[t][h * V + v] = in[t * in_ldt + h * in_ldh + v] * (gate ? sigmoid(gate[t][h * V + v]) : 1): rows laid out head
+// by head ([h][t][v]: in_ldh = tokens * V, in_ldt = V) back into token rows, with the output gate of the mixer applied
+// on the way; or token rows gated where they lie (in == out, in_ldt = ldo, in_ldh = V).
 template <typename T>
-__global__ void heads_to_tokens_kernel(const T* __restrict__ in, const T* __restrict__ gate, long ldg, T* __restrict__ out,
+__global__ void heads_to_tokens_kernel(const T* in, long in_ldt, long in_ldh, const T* __restrict__ gate, long ldg, T* out,
                                        long ldo, int n_tokens, int H, int V)
 {
     fx_pdl_wait();
@@ -161,7 +165,7 @@ __global__ void heads_to_tokens_kernel(const T* __restrict__ in, const T* __rest
         const int t = (int)(idx / (H * V));
         const int c = (int)(idx - (long)t * H * V);
         const int h = c / V, v = c - h * V;
-        float x = to_f32(in[((long)h * n_tokens + t) * V + v]);
+        float x = to_f32(in[(long)t * in_ldt + (long)h * in_ldh + v]);
         if (gate) x *= 1.0f / (1.0f + expf(-to_f32(gate[(long)t * ldg + c])));
         out[(long)t * ldo + c] = from_f32<T>(x);
     }
@@ -196,7 +200,7 @@ extern "C" int fx_qk_norm_store(void* qkv, int dtype, long ld, const int* positi
     return fx_launch_status();
 }
 
-extern "C" int fx_latent_prep(const void* q, long ldq, const void* dkv, long ld_dkv, int dtype, const int* positions,
+extern "C" int fx_latent_prep(void* q, long ldq, const void* dkv, long ld_dkv, int dtype, const int* positions,
                               const int* token_seq, const int* seq_slot, const void* wc, int w_dtype, float eps,
                               const float* cos_sin, int rot_dims, void* q_plain, void* q_full, void* pages,
                               const int* block_table, int table_width, int page_size, int n_tokens, int n_heads,
@@ -208,7 +212,7 @@ extern "C" int fx_latent_prep(const void* q, long ldq, const void* dkv, long ld_
     cudaStream_t s = (cudaStream_t)stream;
     const int nt = threads_for_width(n_heads * plain_dim > rank ? n_heads * plain_dim : rank);
 #define FX_GO(T)                                                                                                      \
-    fx_launch_pdl(latent_prep_kernel<T>, n_tokens, nt, 0, s, (const T*)q, ldq, (const T*)dkv, ld_dkv, positions,      \
+    fx_launch_pdl(latent_prep_kernel<T>, n_tokens, nt, 0, s, (T*)q, ldq, (const T*)dkv, ld_dkv, positions,      \
                   token_seq, seq_slot, wc, w_dtype, eps, cos_sin, rot_dims, (T*)q_plain, (T*)q_full, (T*)pages,       \
                   block_table, table_width, page_size, n_tokens, n_heads, plain_dim, rot_dim, rank, write_cache, status)
     if (dtype == FX_F32) FX_GO(float);
@@ -235,18 +239,18 @@ extern "C" int fx_rmsnorm_rows(const void* x, int x_dtype, long ldx, const void*
     return fx_launch_status();
 }
 
-extern "C" int fx_heads_to_tokens(const void* in, const void* gate, long ldg, void* out, long ldo, int dtype,
-                                  int n_tokens, int n_heads, int width, void* stream)
+extern "C" int fx_heads_to_tokens(const void* in, long in_ldt, long in_ldh, const void* gate, long ldg, void* out, long ldo,
+                                  int dtype, int n_tokens, int n_heads, int width, void* stream)
 {
     if (n_tokens <= 0 || n_heads <= 0 || width <= 0) return FX_OK;
     cudaStream_t s = (cudaStream_t)stream;
     long blocks = fx_cdiv((long)n_tokens * n_heads * width, 256);
     if (blocks > fx_sm_count() * 16L) blocks = fx_sm_count() * 16L;
     if (dtype == FX_F32)
-        fx_launch_pdl(heads_to_tokens_kernel<float>, (unsigned)blocks, 256, 0, s, (const float*)in, (const float*)gate, ldg,
+        fx_launch_pdl(heads_to_tokens_kernel<float>, (unsigned)blocks, 256, 0, s, (const float*)in, in_ldt, in_ldh, (const float*)gate, ldg,
                       (float*)out, ldo, n_tokens, n_heads, width);
     else if (dtype == FX_BF16)
-        fx_launch_pdl(heads_to_tokens_kernel<bf16>, (unsigned)blocks, 256, 0, s, (const bf16*)in, (const bf16*)gate, ldg,
+        fx_launch_pdl(heads_to_tokens_kernel<bf16>, (unsigned)blocks, 256, 0, s, (const bf16*)in, in_ldt, in_ldh, (const bf16*)gate, ldg,
                       (bf16*)out, ldo, n_tokens, n_heads, width);
     else return FX_ERR_DTYPE;
     return fx_launch_status();

@@ -50,13 +50,13 @@ _SIGNATURES = {
     "fx_paged_attention_ex": [_P, _L, _L, _P, _P, _L, _L, _I, _P, _I, _I, _P, _P, _P, _P, _L, _L, _I, _I, _I, _I, _I, _I, _F,
                               _F, _P, _P],
     "fx_general_attention_ok": [_I, _I, _I],
-    "fx_general_attention": [_P, _L, _L, _P, _P, _L, _L, _P, _I, _I, _P, _P, _P, _P, _I, _P, _L, _L, _I, _I, _I, _I, _I, _F,
-                             _P, _I, _P, _P, _P],
+    "fx_general_attention": [_P, _L, _L, _P, _P, _L, _L, _P, _P, _I, _I, _P, _P, _P, _P, _I, _P, _L, _L, _I, _I, _I, _I, _I,
+                             _F, _P, _I, _P, _P, _P],
     "fx_qk_norm_store": [_P, _I, _L, _P, _P, _P, _P, _P, _I, _F, _F, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "fx_latent_prep": [_P, _L, _P, _L, _I, _P, _P, _P, _P, _I, _F, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P,
                        _P],
     "fx_rmsnorm_rows": [_P, _I, _L, _P, _I, _F, _P, _I, _L, _I, _I, _P],
-    "fx_heads_to_tokens": [_P, _P, _L, _P, _L, _I, _I, _I, _I, _P],
+    "fx_heads_to_tokens": [_P, _L, _L, _P, _L, _P, _L, _I, _I, _I, _I, _P],
     "fx_route_small": [_P, _L, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P],
     "fx_route": [_P, _L, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _P],
     "fx_route_fused": [_P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _P, _L, _P, _P, _P, _P, _P, _P, _I, _P, _L, _P],
@@ -530,14 +530,23 @@ def paged_attention_ex(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, block_table, pa
 GENERAL_TILE_ROWS = 64     # (token, head) pairs a tile of the tensor-core kernel of the general form holds
 
 
-def general_attention_ok(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, out, ldo, ldoh, key_dim, value_dim) -> int:
+def general_attention_ok(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, out, ldo, ldoh, key_dim, value_dim,
+                         kv_strides=None) -> int:
     """Whether :func:`general_attention` takes these operands (bfloat16, widths in steps of 16, 16-byte rows): 0, or
     how many of its blocks an SM holds."""
-    alias = int(v_pages.data_ptr() == k_pages.data_ptr() and ldv == ldk and value_dim <= key_dim)
+    alias = int(v_pages.data_ptr() == k_pages.data_ptr() and ldv == ldk and value_dim <= key_dim
+                and (kv_strides is None or tuple(kv_strides[:2]) == tuple(kv_strides[2:])))
+    if kv_strides is not None and any(int(x) % 8 for x in kv_strides):
+        return 0
     return int(q.dtype == torch.bfloat16 and k_pages.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
             and ldq % 8 == 0 and ldqh % 8 == 0 and ldk % 8 == 0 and ldv % 8 == 0 and ldo % 2 == 0 and ldoh % 2 == 0
             and q.data_ptr() % 16 == 0 and k_pages.data_ptr() % 16 == 0 and v_pages.data_ptr() % 16 == 0
             and out.data_ptr() % 4 == 0 and _get("fx_general_attention_ok")(key_dim, value_dim, alias))
+
+
+def general_attention_fits(key_dim: int, value_dim: int) -> bool:
+    """Whether the tensor-core kernel of the general form holds rows of these widths at all (separate keys and values)."""
+    return bool(_get("fx_general_attention_ok")(int(key_dim), int(value_dim), 0))
 
 
 def general_attention_items(entries, n_heads: int, n_kv_heads: int):
@@ -563,18 +572,22 @@ def general_attention_items(entries, n_heads: int, n_kv_heads: int):
 
 def general_attention(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, block_table, page_size, positions, token_seq, seq_slot,
                       items, out, ldo, ldoh, n_heads, n_kv_heads, key_dim, value_dim, window, scale, slopes=None,
-                      stream=None, n_splits=1, part_o=None, part_ml=None):
+                      stream=None, n_splits=1, part_o=None, part_ml=None, kv_strides=None):
     """:func:`paged_attention_ex` in bfloat16 on the tensor cores (see :func:`general_attention_ok`).  ``items``: the
     device copy of :func:`general_attention_items`, or None when every entry brings one token (a tile a token and
     kv head; nothing comes from the host, so a captured step replays unchanged).  ``n_splits`` > 1 (without items):
     every token's visible keys are cut into that many runs, a block each; ``part_o`` float32 [T, heads, n_splits,
-    value_dim] and ``part_ml`` float32 [T, heads, n_splits, 2] are scratch, and a second kernel adds the runs up."""
+    value_dim] and ``part_ml`` float32 [T, heads, n_splits, 2] are scratch, and a second kernel adds the runs up.
+    ``kv_strides`` = (k page stride, k head stride, v page stride, v head stride) in elements, for keys and values that
+    do not lie [page][kv head][position][ld] (rows that hold all heads side by side); ``ldk`` / ``ldv`` stay the
+    distance between two positions."""
+    strides = (ctypes.c_long * 4)(*[int(x) for x in kv_strides]) if kv_strides is not None else None
     global _launches
     n = items.shape[0] if items is not None else positions.numel()
     if n_splits > 1:
         _launches += 1
     call("fx_general_attention", _ptr(q), int(ldq), int(ldqh), _ptr(k_pages), _ptr(v_pages), int(ldk), int(ldv),
-         _ptr(block_table), block_table.shape[1], page_size, _ptr(positions), _ptr(token_seq), _ptr(seq_slot),
+         ctypes.cast(strides, c_void_p) if strides is not None else None, _ptr(block_table), block_table.shape[1], page_size, _ptr(positions), _ptr(token_seq), _ptr(seq_slot),
          _ptr(items), n, _ptr(out), int(ldo), int(ldoh), n_heads, n_kv_heads, key_dim, value_dim, int(window or 0),
          float(scale), _ptr(slopes), int(n_splits), _ptr(part_o), _ptr(part_ml),
          stream if stream is not None else stream_ptr())
@@ -601,7 +614,8 @@ def latent_prep(q, dkv, positions, token_seq, seq_slot, c_weight, eps, cos_sin, 
     """The step between a latent attention's projections and its attention kernel: ``dkv`` rows [rank | rot_dim] become
     the cached row (the latent normed with ``c_weight``, the key part rotated on neighbouring pairs by ``cos_sin``
     [T, rot_dims / 2, 2]); ``q`` rows of heads [plain_dim | rot_dim] are split into ``q_plain`` [heads, T, plain_dim]
-    and the rotated part in columns rank.. of ``q_full`` [heads, T, rank + rot_dim]."""
+    and the rotated part in columns rank.. of ``q_full`` [heads, T, rank + rot_dim].  ``q_plain`` None (and ``q_full``
+    None): the queries stay token rows and their rotated parts are turned where they lie."""
     T = q.shape[0]
     call("fx_latent_prep", _ptr(q), _rows(q), _ptr(dkv), _rows(dkv), code(q), _ptr(positions), _ptr(token_seq),
          _ptr(seq_slot), _ptr(c_weight), code(c_weight), float(eps), _ptr(cos_sin), int(rot_dims), _ptr(q_plain),
@@ -623,9 +637,20 @@ def heads_to_tokens(x, out, gate=None, stream=None):
     H, T, V = x.shape
     if not x.is_contiguous() or (gate is not None and gate.dtype != x.dtype) or out.dtype != x.dtype:
         raise KernelError("heads_to_tokens: contiguous [heads, tokens, width] and one element type")
-    call("fx_heads_to_tokens", _ptr(x), _ptr(gate), _rows(gate) if gate is not None else 0, _ptr(out), _rows(out), code(x),
-         T, H, V, stream if stream is not None else stream_ptr())
+    call("fx_heads_to_tokens", _ptr(x), V, T * V, _ptr(gate), _rows(gate) if gate is not None else 0, _ptr(out), _rows(out),
+         code(x), T, H, V, stream if stream is not None else stream_ptr())
     return out
+
+
+def gate_heads_(x, gate, n_heads, stream=None):
+    """x[t, c] *= sigmoid(gate[t, c]) over token rows of ``n_heads`` heads, in place (the same kernel as
+    :func:`heads_to_tokens`, reading the rows where they lie)."""
+    T, W = x.shape
+    if gate.dtype != x.dtype or W % n_heads:
+        raise KernelError("gate_heads_: one element type, a width that the heads divide")
+    call("fx_heads_to_tokens", _ptr(x), _rows(x), W // n_heads, _ptr(gate), _rows(gate), _ptr(x), _rows(x), code(x), T,
+         n_heads, W // n_heads, stream if stream is not None else stream_ptr())
+    return x
 
 
 PREFILL_TILE = 64

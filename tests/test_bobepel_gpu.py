@@ -161,16 +161,28 @@ def test_attention_reads_a_key_far_back_and_its_bias_is_the_distance(dtype):
         assert rel(a, b) < tol
 
 
+@pytest.fixture(params=["latent rows", "expanded"])
+def prompt_form(request, monkeypatch):
+    """Prompt portions of a latent attention in bfloat16 read the latent rows or keys and values expanded from them,
+    whichever is estimated cheaper: force either."""
+    from ferrox_b200.parts import latent_attention
+
+    monkeypatch.setattr(latent_attention, "EXPANDED_MAX_COST_RATIO", 1e9 if request.param == "expanded" else 0.0)
+    return request.param
+
+
 @pytest.mark.parametrize("cut", list(CUTS))
 @pytest.mark.parametrize("H,D,R,rot,V,C,window,q_rank,page", [
     (4, 16, 32, 16, 16, 48, 21, None, 4), (3, 12, 6, 4, 20, 40, 1, None, 8), (2, 24, 8, 8, 28, 36, None, 20, 4),
     (8, 64, 64, 64, 64, 192, 64, None, 64), (4, 32, 32, 32, 64, 128, 65, 96, 64), (2, 16, 16, 0, 16, 32, 40, None, 16)])
 @pytest.mark.parametrize("dtype", list(DTYPES))
-def test_latent_attention_alone_at_its_window_edges(dtype, H, D, R, rot, V, C, window, q_rank, page, cut):
+def test_latent_attention_alone_at_its_window_edges(dtype, H, D, R, rot, V, C, window, q_rank, page, cut, prompt_form):
     """Both latent mixers, windows of one, of a page, of a page and one, none; a loud row at position 5 whose rotated
     key part and latent stand out while it is inside the window: the plain implementation tells the positions just
     inside from those just outside, and the engine agrees with it at all of them."""
     dt, tol = DTYPES[dtype]
+    if prompt_form == "expanded" and (dtype == "float32" or (D + R) % 16 or V % 16):
+        pytest.skip("the expanded form is a bfloat16 path for widths in steps of 16")
     hidden = 64
     spec = latent_spec(hidden, H, D, R, rot, V, C, 0.2, window=window, q_rank=q_rank)
     w = random_tensors(spec, seed=H + C, std=0.25)
@@ -292,8 +304,10 @@ def clear_rows(expected, name, dtype):
 @pytest.mark.parametrize("run", list(RUNS))
 @pytest.mark.parametrize("name", sorted(CONFIGS))
 @pytest.mark.parametrize("dtype", list(DTYPES))
-def test_model_under_every_cut(folders, expected, dtype, name, run):
+def test_model_under_every_cut(folders, expected, dtype, name, run, prompt_form):
     _, tol = DTYPES[dtype]
+    if prompt_form == "expanded" and (dtype == "float32" or name == "B"):
+        pytest.skip("the expanded form is a bfloat16 path for widths in steps of 16")
     eng = engine(folders[name], dtype)
     got = RUNS[run](eng, prompts_for(name))
     compare(got, expected[name][2], tol, f"{name} {dtype} {run}", clear_rows(expected, name, dtype))
