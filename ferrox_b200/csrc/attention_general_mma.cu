@@ -24,7 +24,7 @@
 
 namespace {
 
-constexpr int BQ = 64, BKEY = 32;
+constexpr int BQ = 64;
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
@@ -70,7 +70,8 @@ struct GArgs {
 };
 
 // DVMAX: most value columns one warp accumulates.  NSPLIT: sets of 4 warps that share out the value columns.
-template <int DVMAX, int NSPLIT>
+// BKEY: keys a block of the loop holds.
+template <int DVMAX, int NSPLIT, int BKEY>
 __global__ void __launch_bounds__(128 * NSPLIT) general_attention_kernel(GArgs a)
 {
     constexpr int NTHREADS = 128 * NSPLIT;
@@ -315,10 +316,10 @@ __global__ void general_merge_kernel(const float* __restrict__ part_o, const flo
     }
 }
 
-template <int DVMAX, int NSPLIT>
+template <int DVMAX, int NSPLIT, int BKEY>
 int launch(dim3 grid, size_t smem, cudaStream_t s, const GArgs& a)
 {
-    auto kern = general_attention_kernel<DVMAX, NSPLIT>;
+    auto kern = general_attention_kernel<DVMAX, NSPLIT, BKEY>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
@@ -333,12 +334,24 @@ int launch(dim3 grid, size_t smem, cudaStream_t s, const GArgs& a)
 
 }  // namespace
 
+static size_t general_smem(int key_dim, int value_dim, int alias, int bkey)
+{
+    return (size_t)(BQ + 2 * bkey) * (key_dim * 2 + 16) + (alias ? 0 : (size_t)2 * bkey * (value_dim * 2 + 16));
+}
+
+// Keys a block of the loop: 64 where an SM then still holds three blocks of threads, else 32 (the kernel lives on
+// the warps an SM holds: with 64 keys and two blocks an SM, rows of 192 + 128 elements took 1.6 times as long).
+static int general_bkey(int key_dim, int value_dim, int alias)
+{
+    return general_smem(key_dim, value_dim, alias, 64) + 1024 <= 75 * 1024 ? 64 : 32;
+}
+
 // Whether fx_general_attention takes these sizes (the caller goes to fx_paged_attention_ex otherwise): 0, or how
 // many of its blocks an SM holds.
 extern "C" int fx_general_attention_ok(int key_dim, int value_dim, int alias)
 {
     if (key_dim <= 0 || value_dim <= 0 || key_dim % 16 || value_dim % 16 || key_dim > 640 || value_dim > 512) return 0;
-    const size_t smem = (size_t)(BQ + 2 * BKEY) * (key_dim * 2 + 16) + (alias ? 0 : (size_t)2 * BKEY * (value_dim * 2 + 16));
+    const size_t smem = general_smem(key_dim, value_dim, alias, general_bkey(key_dim, value_dim, alias));
     if (smem > 220 * 1024) return 0;
     const int fit = (int)((227 * 1024) / (smem + 1024));
     return fit > 4 ? 4 : fit;
@@ -376,13 +389,14 @@ extern "C" int fx_general_attention(const void* q, long ldq, long ldqh, const vo
     a.scale_log2e = scale * 1.4426950408889634f; a.slopes = slopes; a.alias = alias;
     a.n_splits = n_splits > 1 ? n_splits : 1; a.part_o = part_o; a.part_ml = part_ml;
     if (a.n_splits > 1 && (items || !part_o || !part_ml || a.n_splits > 65535)) return FX_ERR_SIZE;
-    const size_t smem = (size_t)(BQ + 2 * BKEY) * (key_dim * 2 + 16) + (alias ? 0 : (size_t)2 * BKEY * (value_dim * 2 + 16));
+    const int bkey = general_bkey(key_dim, value_dim, alias);
+    const size_t smem = general_smem(key_dim, value_dim, alias, bkey);
     const int group = n_heads / n_kv_heads;
     dim3 grid = items ? dim3(n_items) : dim3(n_items, n_kv_heads * ((group + BQ - 1) / BQ), a.n_splits);
     cudaStream_t s = (cudaStream_t)stream;
-    if (value_dim <= 64) { a.part_cols = 64; return launch<64, 1>(grid, smem, s, a); }
-    if (value_dim <= 128) { a.part_cols = 128; return launch<128, 1>(grid, smem, s, a); }
-    if (value_dim <= 256) { a.part_cols = ((value_dim / 2 + 15) / 16) * 16; return launch<128, 2>(grid, smem, s, a); }
+    if (value_dim <= 64) { a.part_cols = 64; return bkey == 64 ? launch<64, 1, 64>(grid, smem, s, a) : launch<64, 1, 32>(grid, smem, s, a); }
+    if (value_dim <= 128) { a.part_cols = 128; return bkey == 64 ? launch<128, 1, 64>(grid, smem, s, a) : launch<128, 1, 32>(grid, smem, s, a); }
     a.part_cols = ((value_dim / 2 + 15) / 16) * 16;
-    return launch<256, 2>(grid, smem, s, a);
+    if (value_dim <= 256) return bkey == 64 ? launch<128, 2, 64>(grid, smem, s, a) : launch<128, 2, 32>(grid, smem, s, a);
+    return launch<256, 2, 32>(grid, smem, s, a);
 }

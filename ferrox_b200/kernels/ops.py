@@ -567,6 +567,7 @@ def general_attention_items(entries, n_heads: int, n_kv_heads: int):
                 for c in range(0, group, GENERAL_TILE_ROWS):
                     out.append((flat + i, nt, b, g * group + c, min(GENERAL_TILE_ROWS, group - c)))
         flat += n
+    out.reverse()      # the late tokens of a request see the most keys: their tiles start first
     return np.asarray(out, dtype=np.int32).reshape(-1, 5)
 
 
@@ -1183,7 +1184,7 @@ def grouped_linear(x, w, out, offsets, active, rows_per_group: int, *, status=No
     if tc_ok(x, w) and K % 8 == 0 and N % 8 == 0 and G <= TC_MAX_GROUPS and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0:
         if rows_per_group > 16 or G > TC_SWAP_MAX_GROUPS:
             return gemm_tc(x, w, out, group_offsets=offsets, status=status, stream=stream)
-        if T >= 8:
+        if rows_per_group >= 8 or not (skinny_ok(x, w) and active is not None):
             return gemm_tc_swap(x, w, out, group_offsets=offsets, tokens_per_tile=32 if rows_per_group <= 8 else 64,
                                 weights_first=True, status=status, stream=stream)
     if rows_per_group <= SKINNY_MAX_TOKENS and skinny_ok(x, w) and active is not None:
