@@ -48,7 +48,7 @@ int fx_paged_attention_ex(const void* q, long ldq, long ldqh, const void* k_page
                           int n_heads, int n_kv_heads, int key_dim, int value_dim, int window, float scale, float softcap,
                           const float* slopes, void* stream);
 
-// the same contract in bfloat16 on the tensor cores (attention_general_mma.cu); items: int32 [n_items, 5] = (first flat
+// the same operation in bfloat16 on the tensor cores (attention_general_mma.cu); items: int32 [n_items, 5] = (first flat
 // token, tokens, entry, first query head, heads) or nullptr (one token a tile, n_items = tokens)
 int fx_general_attention_ok(int key_dim, int value_dim, int alias);
 int fx_general_attention(const void* q, long ldq, long ldqh, const void* k_pages, const void* v_pages, long ldk, long ldv,

@@ -1,6 +1,6 @@
 // Attention over pages in its general form, in bfloat16 on the tensor cores: keys and values of different widths
 // (values may be the leading part of the cached key rows), queries and outputs addressed by a token stride and a
-// head stride, an optional bias slope[h] * (i - j) taken off the scores, a window.  The contract of
+// head stride, an optional bias slope[h] * (i - j) taken off the scores, a window.  The operation of
 // fx_paged_attention_ex (attention_generic.cu), for prompt portions and for decoded tokens alike.
 //
 // A tile is 64 ROWS, a row being a (token, query head) pair: consecutive tokens of one request times the query

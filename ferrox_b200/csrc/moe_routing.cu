@@ -253,11 +253,29 @@ __global__ void __launch_bounds__(FUSED_WARPS * 32) route_fused_kernel(FusedArgs
         // the rows in expert order, out of shared memory: a warp a row, 16 bytes a lane and pass
         __syncthreads();
         const int n = n_tokens * a.top_k;
+        const bool scaled = (a.renorm & 4) != 0;     // bit 2 of the mode: every row times its routing weight
         for (int r = warp; r < n; r += FUSED_WARPS) {
             const uint4* src = reinterpret_cast<const uint4*>(x_s) + (long)src_s[r] * n_vec;
             uint4* dst = reinterpret_cast<uint4*>(a.xp_out + (long)r * a.ldxp);
+            if (!scaled) {
 #pragma unroll 4
-            for (int v = lane; v < n_vec; v += 32) dst[v] = src[v];
+                for (int v = lane; v < n_vec; v += 32) dst[v] = src[v];
+                continue;
+            }
+            // (the weights and places were written by this block, before the barrier above)
+            float w = 0.f;
+            for (int k = 0; k < a.top_k; ++k)
+                if (a.inv_perm[(long)src_s[r] * a.top_k + k] == r) w = a.weights[(long)src_s[r] * a.top_k + k];
+            for (int v = lane; v < n_vec; v += 32) {
+                uint4 u = src[v];
+                __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 f = __bfloat1622float2(h2[e]);
+                    h2[e] = __floats2bfloat162_rn(w * f.x, w * f.y);
+                }
+                dst[v] = u;
+            }
         }
     }
 }

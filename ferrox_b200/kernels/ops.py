@@ -456,7 +456,8 @@ def route_fused(x, w_route, logits, top_k, renorm, ids, weights, offsets, src_to
     """What stands between the norm and the experts in a step of a few tokens, in one launch of one thread-block
     cluster (see :func:`route_fused_ok`): the router's product logits = x . w_route^T (32-bit sums; ``w_route`` may carry
     rows beyond the experts', whose logits later kernels read), :func:`route_small` on the first ``n_experts`` columns
-    and, with ``xp_out`` [tokens * top_k, hidden], the rows of ``x`` copied into expert order."""
+    and, with ``xp_out`` [tokens * top_k, hidden], the rows of ``x`` copied into expert order (bit 2 of ``renorm``, value
+    4: each row multiplied by its routing weight on the way)."""
     T, H = x.shape
     R = w_route.shape[0]
     E = n_experts or R

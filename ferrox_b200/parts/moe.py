@@ -177,8 +177,8 @@ class SoftmaxTopkMoe(FeedForward):
             # The cluster's kernel goes first: it needs eight free SMs of one GPC at once, which it finds now and would
             # not find once the shared expert's weight-streaming kernels (enqueued right after it, waiting only for what
             # was before it) fill every SM.
-            xp = rt.empty(T * K, H) if tiles is not None and not scaled else None
-            ops.route_fused(x, self.w_route, logits, K, mode, ids, weights, offsets, src_token, inv_perm, active,
+            xp = rt.empty(T * K, H) if tiles is not None or scaled else None
+            ops.route_fused(x, self.w_route, logits, K, mode | (4 if scaled else 0), ids, weights, offsets, src_token, inv_perm, active,
                             n_experts=E, xp_out=xp, stream=st)
             if overlap:
                 shared = self._shared_on_side(x, batch)
@@ -193,8 +193,9 @@ class SoftmaxTopkMoe(FeedForward):
 
         act = rt.empty(T * K, I)
         y = rt.empty(T * K, H)
-        if scaled:
-            # the routing weight goes into the expert's input: rows scaled on their way into expert order
+        if scaled and xp is None:
+            # the routing weight goes into the expert's input: rows scaled on their way into expert order (the
+            # one-cluster routing kernel of a small step has done it already)
             xp = rt.empty(T * K, H)
             ops.gather_rows_scaled(x, src_token, inv_perm, weights, xp, stream=st)
         if tiles is not None:

@@ -44,7 +44,7 @@ _A0 = attention(4, 2, 32, 48, 0.21, 0.5, 8, moe(6, 2, 32, 1.0, 64, 0.7))
 _A1 = latent(4, 16, 32, 16, 10000.0, 16, 48, 0.17, moe(6, 2, 32, 1.0, 64, 0.7), window=21)
 BOBEPEL_A = {
     "architecture": ARCH, "vocab": 211, "width": 64, "norm": {"eps": 1e-5},
-    "layers": [_A0, _A1, latent(2, 32, 16, 16, 500000.0, 32, 64, 0.2, moe(4, 1, 48, 2.5), q_rank=32),
+    "layers": [_A0, _A1, latent(2, 32, 16, 16, 300000.0, 32, 64, 0.2, moe(4, 1, 48, 2.5), q_rank=32),
                shares(_A0, 0), shares(_A1, 1)],
 }
 
@@ -65,8 +65,8 @@ BOBEPEL_B = {
 BOBEPEL_C = {
     "architecture": ARCH, "vocab": 131, "width": 128, "norm": {"eps": 1e-6},
     "layers": [
-        attention(8, 1, 128, 64, 0.09, 0.3, 64, moe(8, 2, 64, 1.5, 128, 2.0), window=70),
-        latent(8, 64, 64, 64, 500000.0, 64, 192, 0.1, moe(8, 2, 64, 1.5, 128, 2.0)),
+        attention(8, 1, 128, 64, 0.09, 0.35, 64, moe(8, 2, 64, 1.25, 128, 1.75), window=70),
+        latent(8, 64, 64, 64, 250000.0, 64, 192, 0.1, moe(8, 2, 64, 1.25, 128, 1.75)),
         latent(4, 32, 32, 32, 10000.0, 64, 128, 0.15, None, window=65, q_rank=96),
     ],
 }
