@@ -466,7 +466,7 @@ inline int threads_for(int n) { int t = 32; while (t < n && t < 1024) t <<= 1; r
 template <typename T>
 __global__ void gather_rows_scaled_kernel(const T* __restrict__ x, long ldx, const int* __restrict__ rows,
                                           const int* __restrict__ inv_perm, const float* __restrict__ weights,
-                                          int top_k, T* __restrict__ out, long ldo, int width)
+                                          int top_k, T* __restrict__ out, long ldo, int width, int vec_ok)
 {
     fx_pdl_wait();
     const int r = blockIdx.x;
@@ -476,6 +476,17 @@ __global__ void gather_rows_scaled_kernel(const T* __restrict__ x, long ldx, con
         if (inv_perm[(long)t * top_k + k] == r) w = weights[(long)t * top_k + k];
     const T* src = x + (long)t * ldx;
     T* dst = out + (long)r * ldo;
+    if (vec_ok) {      // 16 bytes a thread and pass
+        constexpr int V = 16 / sizeof(T);
+        for (int i = threadIdx.x; i < width / V; i += blockDim.x) {
+            uint4 u = reinterpret_cast<const uint4*>(src)[i];
+            T* e = reinterpret_cast<T*>(&u);
+#pragma unroll
+            for (int j = 0; j < V; ++j) e[j] = from_f32<T>(w * to_f32(e[j]));
+            reinterpret_cast<uint4*>(dst)[i] = u;
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = from_f32<T>(w * to_f32(src[i]));
 }
 
@@ -649,12 +660,15 @@ extern "C" int fx_gather_rows_scaled(const void* x, long ldx, const int* rows, c
 {
     if (n_rows <= 0 || width <= 0) return FX_OK;
     cudaStream_t s = (cudaStream_t)stream;
+    const int es = dtype == FX_F32 ? 4 : 2;
+    const int vec_ok = (width * es) % 16 == 0 && (ldx * es) % 16 == 0 && (ldo * es) % 16 == 0 &&
+                       (uintptr_t)x % 16 == 0 && (uintptr_t)out % 16 == 0;
     if (dtype == FX_F32)
         fx_launch_pdl(gather_rows_scaled_kernel<float>, n_rows, 128, 0, s, (const float*)x, ldx, rows, inv_perm, weights, top_k,
-                      (float*)out, ldo, width);
+                      (float*)out, ldo, width, vec_ok);
     else if (dtype == FX_BF16)
         fx_launch_pdl(gather_rows_scaled_kernel<bf16>, n_rows, 128, 0, s, (const bf16*)x, ldx, rows, inv_perm, weights, top_k,
-                      (bf16*)out, ldo, width);
+                      (bf16*)out, ldo, width, vec_ok);
     else return FX_ERR_DTYPE;
     return fx_launch_status();
 }
