@@ -5,7 +5,6 @@ sequences at a time, no cache.  It shares no code with the engine; the tests com
 """
 from __future__ import annotations
 
-import math
 
 import torch
 

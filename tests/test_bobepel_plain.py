@@ -7,7 +7,7 @@ import pytest
 import torch
 
 import plain_bobepel as pb
-from bobepel_configs import BOBEPEL_A, BOBEPEL_B, BOBEPEL_C, CONFIGS
+from bobepel_configs import BOBEPEL_A, BOBEPEL_B, CONFIGS
 
 
 def resolve(cfg):
