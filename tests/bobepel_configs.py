@@ -65,8 +65,8 @@ BOBEPEL_B = {
 BOBEPEL_C = {
     "architecture": ARCH, "vocab": 131, "width": 128, "norm": {"eps": 1e-6},
     "layers": [
-        attention(8, 1, 128, 64, 0.09, 0.35, 64, moe(8, 2, 64, 1.25, 128, 1.75), window=70),
-        latent(8, 64, 64, 64, 250000.0, 64, 192, 0.1, moe(8, 2, 64, 1.25, 128, 1.75)),
+        attention(8, 1, 128, 64, 0.09, 0.35, 64, moe(8, 2, 96, 1.25, 160, 1.75), window=70),
+        latent(8, 64, 64, 64, 250000.0, 64, 192, 0.1, moe(8, 2, 96, 1.25, 160, 1.75)),
         latent(4, 32, 32, 32, 10000.0, 64, 128, 0.15, None, window=65, q_rank=96),
     ],
 }
