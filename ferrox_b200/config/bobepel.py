@@ -26,8 +26,8 @@ _TOP = (
     Key("max_positions", int, default=DEFAULT_MAX_POSITIONS, check=positive),
 )
 _ATTENTION = (
-    Key("heads", int, check=positive), Key("kv_heads", int, check=positive), Key("dim", int, check=positive),
-    Key("vdim", int, check=positive), Key("scale", float), Key("q_temp", object, default=None, nullable=True),
+    Key("heads", int, check=positive), Key("kv_heads", int, default=lambda v: v["heads"], check=positive),
+    Key("dim", int, check=positive), Key("vdim", int, default=lambda v: v["dim"], check=positive), Key("scale", float), Key("q_temp", object, default=None, nullable=True),
     Key("mask", object, default=None, nullable=True),
 )
 _LATENT = (
