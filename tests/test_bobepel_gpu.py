@@ -119,7 +119,8 @@ def test_experts_weighted_on_their_input_alone(dtype, tokens, top, shared):
 
 
 @pytest.mark.parametrize("cut", list(CUTS))
-@pytest.mark.parametrize("H,G,D,V,page", [(4, 2, 32, 48, 4), (3, 3, 20, 12, 8), (8, 1, 128, 64, 64), (6, 1, 24, 40, 16)])
+@pytest.mark.parametrize("H,G,D,V,page", [(4, 2, 32, 48, 4), (3, 3, 20, 12, 8), (8, 1, 128, 64, 64), (6, 1, 24, 40, 16),
+                                          (72, 1, 16, 16, 16)])      # (more heads on a kv head than a tile has rows)
 @pytest.mark.parametrize("dtype", list(DTYPES))
 def test_attention_with_normed_heads_temperature_and_distance_bias_alone(dtype, H, G, D, V, page, cut):
     dt, tol = DTYPES[dtype]
@@ -174,7 +175,8 @@ def prompt_form(request, monkeypatch):
 @pytest.mark.parametrize("cut", list(CUTS))
 @pytest.mark.parametrize("H,D,R,rot,V,C,window,q_rank,page", [
     (4, 16, 32, 16, 16, 48, 21, None, 4), (3, 12, 6, 4, 20, 40, 1, None, 8), (2, 24, 8, 8, 28, 36, None, 20, 4),
-    (8, 64, 64, 64, 64, 192, 64, None, 64), (4, 32, 32, 32, 64, 128, 65, 96, 64), (2, 16, 16, 0, 16, 32, 37, None, 16)])
+    (8, 64, 64, 64, 64, 192, 64, None, 64), (4, 32, 32, 32, 64, 128, 65, 96, 64), (2, 16, 16, 0, 16, 32, 37, None, 16),
+    (66, 16, 16, 16, 16, 32, 33, None, 16)])      # (the last: more heads than a tile has rows)
 @pytest.mark.parametrize("dtype", list(DTYPES))
 def test_latent_attention_alone_at_its_window_edges(dtype, H, D, R, rot, V, C, window, q_rank, page, cut, prompt_form):
     """Both latent mixers, windows of one, of a page, of a page and one, none; a loud row at position 5 whose rotated
